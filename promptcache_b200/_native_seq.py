@@ -1,0 +1,276 @@
+"""ctypes binding of libpromptcache_b200_seq.so (the C ABI in include/promptcache_b200_seq.h): the sequence-batch kernels.
+
+Like `_native`, this is the only way the Python host reaches these kernels, and there is no CPU or eager fallback: a
+missing library is built on first use (nvcc, sm_100a), a CPU tensor or a failed launch raises `NativeError`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+from ._native import NativeError, note_replayed_launches  # noqa: F401  (one error type for both libraries)
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpromptcache_b200_seq.so")
+PCS_BF16, PCS_F32 = 0, 1
+EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu",
+           "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan")
+
+
+class pcs_gna_params(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("g", C.c_void_p), ("y_stride", C.c_int64), ("g_stride", C.c_int64),
+                ("w", C.c_void_p), ("ls", C.c_void_p), ("next_w", C.c_void_p), ("h_out", C.c_void_p),
+                ("n_rows", C.c_int32), ("width", C.c_int32), ("eps", C.c_float), ("dtype", C.c_int32)]
+
+
+class pcs_qkprep_params(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("row_stride", C.c_int64), ("q_off", C.c_int32), ("k_off", C.c_int32), ("v_off", C.c_int32),
+                ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("eps", C.c_float),
+                ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
+                ("temp_coef", C.c_float), ("temp_every", C.c_int32),
+                ("q_out", C.c_void_p), ("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("cap", C.c_int32),
+                ("v_first_pool", C.c_void_p), ("v_lambda", C.c_void_p),
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p),
+                ("n_tokens", C.c_int32), ("dtype", C.c_int32)]
+
+
+class pcs_attn_params(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("out", C.c_void_p),
+                ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("cap", C.c_int32),
+                ("scale", C.c_float), ("bias_r1", C.c_void_p), ("bias_r2", C.c_void_p), ("sink", C.c_int32),
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p),
+                ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
+                ("n_tokens", C.c_int32), ("n_seqs", C.c_int32), ("max_len", C.c_int32), ("dtype", C.c_int32),
+                ("impl", C.c_int32), ("reserved", C.c_int32)]
+
+
+class pcs_mlstm_params(C.Structure):
+    _fields_ = [("proj", C.c_void_p), ("row_stride", C.c_int64),
+                ("q_off", C.c_int32), ("k_off", C.c_int32), ("v_off", C.c_int32), ("g_off", C.c_int32),
+                ("ig", C.c_void_p), ("fg", C.c_void_p), ("norm_w", C.c_void_p), ("out", C.c_void_p),
+                ("s_pool", C.c_void_p), ("n_pool", C.c_void_p), ("m_pool", C.c_void_p),
+                ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("q_scale", C.c_float), ("eps", C.c_float),
+                ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p), ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
+                ("n_seqs", C.c_int32), ("dtype", C.c_int32), ("max_len", C.c_int32), ("impl", C.c_int32)]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def load() -> C.CDLL:
+    """dlopen the in-tree library, building it first when it is missing or older than its sources."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    from . import build as _build
+    try:
+        path = _build.build_seq()
+    except Exception as e:  # no compiler: a library that travelled with the tree is still usable
+        if not os.path.exists(LIB_PATH):
+            raise NativeError(f"{LIB_PATH} is missing and could not be built: {e}") from e
+        path = LIB_PATH
+    lib = C.CDLL(path, mode=C.RTLD_LOCAL)
+    lib.pcs_version.restype = C.c_int
+    lib.pcs_last_error.restype = C.c_char_p
+    lib.pcs_launch_count.restype = C.c_int64
+    lib.pcs_embed.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    lib.pcs_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    lib.pcs_gate_norm_add.argtypes = [C.POINTER(pcs_gna_params), C.c_void_p]
+    lib.pcs_xielu.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.pcs_qk_prep.argtypes = [C.POINTER(pcs_qkprep_params), C.c_void_p]
+    lib.pcs_attn.argtypes = [C.POINTER(pcs_attn_params), C.c_void_p]
+    lib.pcs_mlstm_gates.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    lib.pcs_mlstm_scan.argtypes = [C.POINTER(pcs_mlstm_params), C.c_void_p]
+    for name in EXPORTS[3:]:
+        getattr(lib, name).restype = C.c_int
+    _lib = lib
+    return lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{what} failed ({rc}): {load().pcs_last_error().decode('utf-8', 'replace')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return PCS_BF16
+    if dtype == torch.float32:
+        return PCS_F32
+    raise NativeError(f"the sequence-batch kernels compute in bfloat16 or float32, not {dtype}")
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise NativeError("promptcache_b200 kernels take CUDA tensors only (no CPU path exists)")
+
+
+def _rows2d(t: torch.Tensor, dtype: torch.dtype, what: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1 or t.dtype != dtype:
+        raise NativeError(f"{what}: expected a 2-D {dtype} tensor with a contiguous inner dimension, got {tuple(t.shape)} {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return t.data_ptr() if t is not None else None
+
+
+def launch_count() -> int:
+    return int(load().pcs_launch_count()) if _lib is not None else 0
+
+
+class Batch:
+    """The int32 description of one step's batch on the device (one host-to-device copy): per token its entry and position,
+    per entry its slot, the tokens the slot already holds, the number of new tokens and the index of the first one."""
+
+    def __init__(self, slots, pos0, lens, device):
+        n_seqs, n_tokens = len(slots), int(sum(lens))
+        offs, tok_seq, tok_pos, o = [], [], [], 0
+        for b, (p0, n) in enumerate(zip(pos0, lens)):
+            offs.append(o)
+            tok_seq += [b] * n
+            tok_pos += range(p0, p0 + n)
+            o += n
+        host = torch.tensor(tok_seq + tok_pos + list(slots) + list(pos0) + list(lens) + offs, dtype=torch.int32)
+        self.meta = host.pin_memory().to(device, non_blocking=True) if device.type == "cuda" else host
+        T, B = n_tokens, n_seqs
+        m = self.meta
+        self.tok_seq, self.tok_pos = m[0:T], m[T:2 * T]
+        self.seq_slot, self.seq_pos0, self.seq_len, self.seq_off = (m[2 * T + i * B:2 * T + (i + 1) * B] for i in range(4))
+        self.n_tokens, self.n_seqs, self.max_len = T, B, max(lens) if lens else 0
+        self.offsets, self.lens, self.pos0, self.slots = offs, list(lens), list(pos0), list(slots)
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float) -> None:
+    _cuda(table, ids, out)
+    if ids.dtype != torch.int64 or not ids.is_contiguous() or out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
+        raise NativeError("embed: ids must be contiguous int64, out contiguous float32, the table contiguous")
+    _check(load().pcs_embed(table.data_ptr(), ids.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1], table.shape[0], float(scale),
+                            dtype_code(table.dtype), _stream()), "pcs_embed")
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rms_norm(x[rows[r]]) * w; x is the 32-bit residual stream, out is in the compute type."""
+    _cuda(x, w, out, rows)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.dtype != w.dtype:
+        raise NativeError("rmsnorm: x must be contiguous float32, out contiguous in the weight's type")
+    if rows is not None and (rows.dtype != torch.int32 or not rows.is_contiguous() or rows.numel() != out.shape[0]):
+        raise NativeError("rmsnorm: rows must be contiguous int32, one per output row")
+    _check(load().pcs_rmsnorm(x.data_ptr(), _ptr(rows), w.data_ptr(), out.data_ptr(), out.shape[0], x.shape[1], float(eps),
+                              dtype_code(w.dtype), _stream()), "pcs_rmsnorm")
+
+
+def gate_norm_add(x: torch.Tensor, y: torch.Tensor, g: Optional[torch.Tensor], w: torch.Tensor, ls: Optional[torch.Tensor], eps: float,
+                  next_w: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None) -> None:
+    """x += ls * w * rms_norm(y * sigmoid(g)); then h_out = rms_norm(x) * next_w when next_w is given."""
+    _cuda(x, y, g, w, ls, next_w, h_out)
+    _rows2d(y, w.dtype, "gate_norm_add: y")
+    if g is not None:
+        _rows2d(g, w.dtype, "gate_norm_add: g")
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.shape != y.shape:
+        raise NativeError("gate_norm_add: x must be contiguous float32 of y's shape")
+    if h_out is not None and (not h_out.is_contiguous() or h_out.dtype != w.dtype):
+        raise NativeError("gate_norm_add: h_out must be contiguous in the compute type")
+    p = pcs_gna_params()
+    p.x, p.y, p.g, p.y_stride, p.g_stride = x.data_ptr(), y.data_ptr(), _ptr(g), y.stride(0), g.stride(0) if g is not None else 0
+    p.w, p.ls, p.next_w, p.h_out = w.data_ptr(), _ptr(ls), _ptr(next_w), _ptr(h_out)
+    p.n_rows, p.width, p.eps, p.dtype = x.shape[0], x.shape[1], float(eps), dtype_code(w.dtype)
+    _check(load().pcs_gate_norm_add(C.byref(p), _stream()), "pcs_gate_norm_add")
+
+
+def xielu(z: torch.Tensor, out: torch.Tensor, a: torch.Tensor) -> None:
+    _cuda(z, out, a)
+    _rows2d(z, a.dtype, "xielu: z")
+    _rows2d(out, a.dtype, "xielu: out")
+    _check(load().pcs_xielu(z.data_ptr(), z.stride(0), out.data_ptr(), out.stride(0), a.data_ptr(), z.shape[0], z.shape[1],
+                            dtype_code(a.dtype), _stream()), "pcs_xielu")
+
+
+def qk_prep(qkv: torch.Tensor, offs, q_norm_w, k_norm_w, eps: float, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
+            temp_coef: float, temp_every: int, q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+            v_first_pool: Optional[torch.Tensor], v_lambda: Optional[torch.Tensor], batch: Batch) -> None:
+    """qkv: [T, *] projections with q / k / v at the column offsets `offs`; pools [slots, Hkv, cap, dim | vdim]."""
+    _cuda(qkv, q_out, k_pool, v_pool)
+    dt = qkv.dtype
+    _rows2d(qkv, dt, "qk_prep: qkv")
+    if not (k_pool.is_contiguous() and v_pool.is_contiguous() and q_out.is_contiguous()) or k_pool.dtype != dt or v_pool.dtype != dt:
+        raise NativeError("qk_prep: pools and q_out must be contiguous tensors of the compute type")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, k_pool.shape[2], dim) or tuple(v_pool.shape[1:]) != (n_kv_heads, k_pool.shape[2], vdim):
+        raise NativeError("qk_prep: pool shapes do not match the head sizes")
+    if v_first_pool is not None and v_first_pool.shape != v_pool.shape:
+        raise NativeError("qk_prep: the mixed-in value pool must have the shape of this layer's value pool")
+    p = pcs_qkprep_params()
+    p.qkv, p.row_stride = qkv.data_ptr(), qkv.stride(0)
+    p.q_off, p.k_off, p.v_off = offs
+    p.q_norm_w, p.k_norm_w, p.eps = _ptr(q_norm_w), _ptr(k_norm_w), float(eps)
+    p.n_heads, p.n_kv_heads, p.dim, p.vdim = n_heads, n_kv_heads, dim, vdim
+    p.temp_coef, p.temp_every = float(temp_coef), int(temp_every)
+    p.q_out, p.k_pool, p.v_pool, p.cap = q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[2]
+    p.v_first_pool, p.v_lambda = _ptr(v_first_pool), _ptr(v_lambda)
+    p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
+    p.n_tokens, p.dtype = batch.n_tokens, dtype_code(dt)
+    _check(load().pcs_qk_prep(C.byref(p), _stream()), "pcs_qk_prep")
+
+
+def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float,
+              r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: bool, batch: Batch, impl: int = 0) -> None:
+    """q [T, H*dim], out [T, H*vdim]; causal over each entry's own slot rows; r1 / r2 float32 [H] or None."""
+    _cuda(q, k_pool, v_pool, out, r1, r2)
+    dt = q.dtype
+    if not (q.is_contiguous() and out.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous()) or out.dtype != dt \
+            or k_pool.dtype != dt or v_pool.dtype != dt:
+        raise NativeError("attention: q, out and the pools must be contiguous tensors of one compute type")
+    for r in (r1, r2):
+        if r is not None and (r.dtype != torch.float32 or r.numel() != n_heads or not r.is_contiguous()):
+            raise NativeError("attention: the distance-bias numbers must be float32 [H]")
+    p = pcs_attn_params()
+    p.q, p.k_pool, p.v_pool, p.out = q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr()
+    p.n_heads, p.n_kv_heads, p.dim, p.vdim, p.cap = n_heads, k_pool.shape[1], k_pool.shape[3], v_pool.shape[3], k_pool.shape[2]
+    p.scale, p.bias_r1, p.bias_r2, p.sink = float(scale), _ptr(r1), _ptr(r2), 1 if sink else 0
+    p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
+    p.seq_pos0, p.seq_len, p.seq_off = batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(), batch.seq_off.data_ptr()
+    p.n_tokens, p.n_seqs, p.max_len, p.dtype, p.impl = batch.n_tokens, batch.n_seqs, batch.max_len, dtype_code(dt), impl
+    _check(load().pcs_attn(C.byref(p), _stream()), "pcs_attn")
+
+
+def mlstm_gates(h: torch.Tensor, w_i: torch.Tensor, w_f: torch.Tensor, b_i: torch.Tensor, b_f: torch.Tensor, ig: torch.Tensor,
+                fg: torch.Tensor, cap: float) -> None:
+    _cuda(h, w_i, w_f, b_i, b_f, ig, fg)
+    _rows2d(h, w_i.dtype, "mlstm_gates: h")
+    if not (w_i.is_contiguous() and w_f.is_contiguous()) or b_i.dtype != torch.float32 or b_f.dtype != torch.float32 \
+            or ig.dtype != torch.float32 or fg.dtype != torch.float32 or not ig.is_contiguous() or not fg.is_contiguous():
+        raise NativeError("mlstm_gates: weights contiguous, biases and gates float32")
+    _check(load().pcs_mlstm_gates(h.data_ptr(), h.stride(0), w_i.data_ptr(), w_f.data_ptr(), b_i.data_ptr(), b_f.data_ptr(),
+                                  ig.data_ptr(), fg.data_ptr(), h.shape[0], h.shape[1], w_i.shape[0], float(cap),
+                                  dtype_code(w_i.dtype), _stream()), "pcs_mlstm_gates")
+
+
+def mlstm_scan(proj: torch.Tensor, offs, ig: torch.Tensor, fg: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor,
+               s_pool: torch.Tensor, n_pool: torch.Tensor, m_pool: torch.Tensor, eps: float, batch: Batch, impl: int = 0) -> None:
+    """proj [T, *] with q / k / v / output-gate columns at `offs`; state pools float32 [slots, H, dim, vdim], [slots, H, dim],
+    [slots, H]; out [T, H*vdim]."""
+    _cuda(proj, ig, fg, norm_w, out, s_pool, n_pool, m_pool)
+    dt = proj.dtype
+    _rows2d(proj, dt, "mlstm_scan: proj")
+    if s_pool.dtype != torch.float32 or n_pool.dtype != torch.float32 or m_pool.dtype != torch.float32 \
+            or not (s_pool.is_contiguous() and n_pool.is_contiguous() and m_pool.is_contiguous() and out.is_contiguous()):
+        raise NativeError("mlstm_scan: the state pools must be contiguous float32")
+    p = pcs_mlstm_params()
+    p.proj, p.row_stride = proj.data_ptr(), proj.stride(0)
+    p.q_off, p.k_off, p.v_off, p.g_off = offs
+    p.ig, p.fg, p.norm_w, p.out = ig.data_ptr(), fg.data_ptr(), norm_w.data_ptr(), out.data_ptr()
+    p.s_pool, p.n_pool, p.m_pool = s_pool.data_ptr(), n_pool.data_ptr(), m_pool.data_ptr()
+    p.heads, p.dim, p.vdim = s_pool.shape[1], s_pool.shape[2], s_pool.shape[3]
+    p.q_scale, p.eps = float(p.dim) ** -0.5, float(eps)
+    p.seq_slot, p.seq_pos0, p.seq_len, p.seq_off = (batch.seq_slot.data_ptr(), batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(),
+                                                    batch.seq_off.data_ptr())
+    p.n_seqs, p.dtype, p.max_len, p.impl = batch.n_seqs, dtype_code(dt), batch.max_len, impl
+    _check(load().pcs_mlstm_scan(C.byref(p), _stream()), "pcs_mlstm_scan")

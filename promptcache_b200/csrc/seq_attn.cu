@@ -1,0 +1,192 @@
+// Attention over the slot pool: query / key preparation with append, and the plain attention kernel.
+//
+// pcs_qk_prep   one block per token: RMS norm over the WHOLE query projection (all heads at once) and over the whole key
+//               projection, query temperature from the token's position, value mixing with the rows an earlier layer
+//               appended for the same token, K / V rows written behind the slot's cached rows.
+// pcs_attn      one block per (token, head): keys in tiles of 128, one key per thread for the score, online softmax in
+//               32-bit, then one value column per thread.  Scores, weights and the accumulator are 32-bit in both types.
+//               A sink is one more term exp(0 - m) of the denominator that has no value: the running maximum starts at 0
+//               and the running sum at 1 instead of (-inf, 0).
+#include "seq_common.cuh"
+
+namespace pcs {
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prep_kernel(const pcs_qkprep_params p) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
+  const T* row = static_cast<const T*>(p.qkv) + static_cast<long long>(t) * p.row_stride;
+  const int nq = p.n_heads * p.dim, nk = p.n_kv_heads * p.dim, nv = p.n_kv_heads * p.vdim;
+  // query
+  {
+    const T* q = row + p.q_off;
+    float inv = 1.f;
+    if (p.q_norm_w) {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = ldf(q + i); ss = fmaf(v, v, ss); }
+      ss = block_sum(ss, red);
+      inv = 1.f / sqrtf(ss / static_cast<float>(nq) + p.eps);
+    }
+    float temp = 1.f;
+    if (p.temp_every > 0) temp = 1.f + p.temp_coef * logf(static_cast<float>((pos + 1) / p.temp_every) + 1.f);
+    const T* w = static_cast<const T*>(p.q_norm_w);
+    T* qo = static_cast<T*>(p.q_out) + static_cast<long long>(t) * nq;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+      float v = ldf(q + i) * inv;
+      if (w) v *= ldf(w + i);
+      stf(qo + i, v * temp);
+    }
+  }
+  // key
+  {
+    const T* k = row + p.k_off;
+    float inv = 1.f;
+    if (p.k_norm_w) {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = ldf(k + i); ss = fmaf(v, v, ss); }
+      ss = block_sum(ss, red);
+      inv = 1.f / sqrtf(ss / static_cast<float>(nk) + p.eps);
+    }
+    const T* w = static_cast<const T*>(p.k_norm_w);
+    T* kp = static_cast<T*>(p.k_pool) + static_cast<long long>(slot) * p.n_kv_heads * p.cap * p.dim;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+      float v = ldf(k + i) * inv;
+      if (w) v *= ldf(w + i);
+      const int g = i / p.dim, d = i - g * p.dim;
+      stf(kp + (static_cast<long long>(g) * p.cap + pos) * p.dim + d, v);
+    }
+  }
+  // value
+  {
+    const T* v = row + p.v_off;
+    const long long base = static_cast<long long>(slot) * p.n_kv_heads * p.cap * p.vdim;
+    T* vp = static_cast<T*>(p.v_pool) + base;
+    const T* vf = p.v_first_pool ? static_cast<const T*>(p.v_first_pool) + base : nullptr;
+    const float lam = vf ? ldf(static_cast<const T*>(p.v_lambda)) : 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const int g = i / p.vdim, d = i - g * p.vdim;
+      const long long o = (static_cast<long long>(g) * p.cap + pos) * p.vdim + d;
+      float x = ldf(v + i);
+      if (vf) x = (1.f - lam) * x + lam * ldf(vf + o);
+      stf(vp + o, x);
+    }
+  }
+}
+
+constexpr int kAttnThreads = 128;
+constexpr int kAttnMaxVPT = 4;  // value columns per thread: vdim <= 512
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn_params p) {
+  extern __shared__ float sm[];  // q[dim], w[128]
+  __shared__ float red[33];
+  float* qs = sm;
+  float* ws = sm + p.dim;
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
+  const int g = h / (p.n_heads / p.n_kv_heads);
+  const int D = p.dim, V = p.vdim;
+  const T* q = static_cast<const T*>(p.q) + (static_cast<long long>(t) * p.n_heads + h) * D;
+  const T* K = static_cast<const T*>(p.k_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * D;
+  const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
+  for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
+  const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
+  float m = p.sink ? 0.f : -INFINITY, l = p.sink ? 1.f : 0.f;
+  float acc[kAttnMaxVPT] = {0.f, 0.f, 0.f, 0.f};
+  const bool vec = (D % Vec<T>::n) == 0;
+  __syncthreads();
+  const int n_keys = pos + 1;
+  for (int j0 = 0; j0 < n_keys; j0 += kAttnThreads) {
+    const int j = j0 + tid;
+    float s = -INFINITY;
+    if (j < n_keys) {
+      const T* kr = K + static_cast<long long>(j) * D;
+      float a = 0.f;
+      if (vec) {
+        for (int d = 0; d < D; d += Vec<T>::n) {
+          float kv[Vec<T>::n];
+          ld16(kr + d, kv);
+#pragma unroll
+          for (int e = 0; e < Vec<T>::n; ++e) a = fmaf(qs[d + e], kv[e], a);
+        }
+      } else {
+        for (int d = 0; d < D; ++d) a = fmaf(qs[d], ldf(kr + d), a);
+      }
+      s = a * p.scale;
+      if (p.bias_r1) s -= r1 * log1pf(r2 * static_cast<float>(pos - j));
+    }
+    const float tmax = block_max(s, red);
+    const float m_new = fmaxf(m, tmax);
+    const float f = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    const float w = (j < n_keys) ? expf(s - m_new) : 0.f;
+    ws[tid] = w;
+    const float tsum = block_sum(w, red);  // its barriers also publish ws
+    l = l * f + tsum;
+    m = m_new;
+    const int nt = min(kAttnThreads, n_keys - j0);
+#pragma unroll
+    for (int u = 0; u < kAttnMaxVPT; ++u) {
+      const int c = tid + u * kAttnThreads;
+      if (c < V) {
+        float a = acc[u] * f;
+        const T* vr = Vp + static_cast<long long>(j0) * V + c;
+        for (int jj = 0; jj < nt; ++jj) a = fmaf(ws[jj], ldf(vr + static_cast<long long>(jj) * V), a);
+        acc[u] = a;
+      }
+    }
+    __syncthreads();  // ws is rewritten by the next tile
+  }
+  T* o = static_cast<T*>(p.out) + (static_cast<long long>(t) * p.n_heads + h) * V;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int u = 0; u < kAttnMaxVPT; ++u) {
+    const int c = tid + u * kAttnThreads;
+    if (c < V) stf(o + c, acc[u] * inv);
+  }
+}
+
+}  // namespace pcs
+
+PCS_API int pcs_qk_prep(const pcs_qkprep_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_qk_prep: null params");
+  if (p->n_tokens == 0) return PCS_OK;
+  PCS_REQUIRE(p->qkv && p->q_out && p->k_pool && p->v_pool && p->tok_seq && p->tok_pos && p->seq_slot, "pcs_qk_prep: null tensor");
+  PCS_REQUIRE(p->n_heads > 0 && p->n_kv_heads > 0 && p->n_heads % p->n_kv_heads == 0 && p->dim > 0 && p->vdim > 0 && p->cap > 0,
+              "pcs_qk_prep: bad sizes H=%d Hkv=%d dim=%d vdim=%d cap=%d", p->n_heads, p->n_kv_heads, p->dim, p->vdim, p->cap);
+  PCS_REQUIRE(p->v_first_pool == nullptr || p->v_lambda != nullptr, "pcs_qk_prep: value mixing needs lambda");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PCS_DISPATCH(p->dtype, pcs::qk_prep_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
+
+namespace pcs {
+int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled);
+}
+
+PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_attn: null params");
+  if (p->n_tokens == 0) return PCS_OK;
+  PCS_REQUIRE(p->q && p->k_pool && p->v_pool && p->out && p->tok_seq && p->tok_pos && p->seq_slot, "pcs_attn: null tensor");
+  PCS_REQUIRE(p->n_heads > 0 && p->n_kv_heads > 0 && p->n_heads % p->n_kv_heads == 0 && p->dim > 0 && p->vdim > 0 && p->cap > 0,
+              "pcs_attn: bad sizes H=%d Hkv=%d dim=%d vdim=%d cap=%d", p->n_heads, p->n_kv_heads, p->dim, p->vdim, p->cap);
+  PCS_REQUIRE(p->vdim <= pcs::kAttnThreads * pcs::kAttnMaxVPT, "pcs_attn: vdim %d exceeds %d", p->vdim,
+              pcs::kAttnThreads * pcs::kAttnMaxVPT);
+  PCS_REQUIRE(p->n_heads <= 65535, "pcs_attn: too many heads");
+  PCS_REQUIRE((p->bias_r1 == nullptr) == (p->bias_r2 == nullptr), "pcs_attn: the distance bias needs both r1 and r2");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->impl == 0) {
+    bool handled = false;
+    if (int rc = pcs::launch_attn_tc(*p, st, &handled)) return rc;
+    if (handled) return PCS_OK;
+  }
+  const size_t smem = static_cast<size_t>(p->dim + pcs::kAttnThreads) * sizeof(float);
+  PCS_REQUIRE(smem <= 48 * 1024, "pcs_attn: dim %d exceeds the shared-memory query row", p->dim);
+  dim3 grid(p->n_tokens, p->n_heads);
+  PCS_DISPATCH(p->dtype, pcs::attn_plain_kernel<T><<<grid, pcs::kAttnThreads, smem, st>>>(*p));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}

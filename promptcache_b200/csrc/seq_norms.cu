@@ -1,0 +1,157 @@
+// Sequence-batch support kernels: error state of the library, embedding, RMS norm, the gated output norm with layer scale
+// and residual sum, xIELU.  The residual stream is 32-bit; statistics and gates are evaluated in 32-bit in both types.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <atomic>
+
+#include "seq_common.cuh"
+
+namespace pcs {
+
+static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) embed_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids,
+                                                    float* __restrict__ out, int width, int vocab, float scale) {
+  const int t = blockIdx.x;
+  long long id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const T* row = table + id * width;
+  float* o = out + static_cast<long long>(t) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = ldf(row + i) * scale;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+                                                      const T* __restrict__ w, T* __restrict__ out, int width, float eps) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* xr = x + static_cast<long long>(rows ? rows[r] : r) * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(width) + eps);
+  T* o = out + static_cast<long long>(r) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) stf(o + i, xr[i] * inv * ldf(w + i));
+}
+
+// One block per row.  u = y * sigmoid(g) is kept in shared memory between the statistics pass and the update.
+template <typename T>
+__global__ void __launch_bounds__(256) gate_norm_add_kernel(const pcs_gna_params p) {
+  extern __shared__ float u[];  // [width]
+  __shared__ float red[33];
+  const int r = blockIdx.x, W = p.width;
+  const T* y = static_cast<const T*>(p.y) + static_cast<long long>(r) * p.y_stride;
+  const T* g = p.g ? static_cast<const T*>(p.g) + static_cast<long long>(r) * p.g_stride : nullptr;
+  const T* w = static_cast<const T*>(p.w);
+  const T* ls = static_cast<const T*>(p.ls);
+  float* x = p.x + static_cast<long long>(r) * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = ldf(y + i);
+    if (g) v *= sigmoidf_(ldf(g + i));
+    u[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(W) + p.eps);
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = u[i] * inv * ldf(w + i);
+    if (ls) v *= ldf(ls + i);
+    const float xn = x[i] + v;
+    x[i] = xn;
+    u[i] = xn;
+    s2 = fmaf(xn, xn, s2);
+  }
+  if (p.next_w == nullptr) return;
+  s2 = block_sum(s2, red);
+  const float inv2 = 1.f / sqrtf(s2 / static_cast<float>(W) + p.eps);
+  const T* nw = static_cast<const T*>(p.next_w);
+  T* h = static_cast<T*>(p.h_out) + static_cast<long long>(r) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) stf(h + i, u[i] * inv2 * ldf(nw + i));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) xielu_kernel(const T* __restrict__ z, long long z_stride, T* __restrict__ out,
+                                                    long long out_stride, const T* __restrict__ a, int width) {
+  const int r = blockIdx.x;
+  const float ap = softplusf_(ldf(a)), an = 0.5f + softplusf_(ldf(a + 1));
+  const T* zr = z + r * z_stride;
+  T* o = out + r * out_stride;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) {
+    const float v = ldf(zr + i);
+    const float f = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+    stf(o + i, f);
+  }
+}
+
+}  // namespace pcs
+
+PCS_API int pcs_version(void) { return PCS_ABI_VERSION; }
+PCS_API const char* pcs_last_error(void) { return pcs::g_err; }
+PCS_API int64_t pcs_launch_count(void) { return pcs::g_launches.load(std::memory_order_relaxed); }
+
+PCS_API int pcs_embed(const void* table, const int64_t* ids, float* out, int n_tokens, int width, int vocab, float scale,
+                      int dtype, void* stream) {
+  if (n_tokens == 0) return PCS_OK;
+  PCS_REQUIRE(table && ids && out && n_tokens > 0 && width > 0 && vocab > 0, "pcs_embed: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PCS_DISPATCH(dtype, pcs::embed_kernel<T><<<n_tokens, 256, 0, st>>>(static_cast<const T*>(table), ids, out, width, vocab, scale));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
+
+PCS_API int pcs_rmsnorm(const float* x, const int32_t* rows, const void* w, void* out, int n_rows, int width, float eps,
+                        int dtype, void* stream) {
+  if (n_rows == 0) return PCS_OK;
+  PCS_REQUIRE(x && w && out && n_rows > 0 && width > 0, "pcs_rmsnorm: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PCS_DISPATCH(dtype, pcs::rmsnorm_kernel<T><<<n_rows, 256, 0, st>>>(x, rows, static_cast<const T*>(w), static_cast<T*>(out), width, eps));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
+
+PCS_API int pcs_gate_norm_add(const pcs_gna_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_gate_norm_add: null params");
+  if (p->n_rows == 0) return PCS_OK;
+  PCS_REQUIRE(p->x && p->y && p->w && p->n_rows > 0 && p->width > 0, "pcs_gate_norm_add: bad arguments");
+  PCS_REQUIRE(p->next_w == nullptr || p->h_out != nullptr, "pcs_gate_norm_add: next_w needs h_out");
+  const size_t smem = static_cast<size_t>(p->width) * sizeof(float);
+  PCS_REQUIRE(smem <= 200 * 1024, "pcs_gate_norm_add: width %d exceeds the shared-memory row", p->width);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024) {
+    PCS_DISPATCH(p->dtype, PCS_CHECK_CUDA(cudaFuncSetAttribute(pcs::gate_norm_add_kernel<T>,
+                                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
+  }
+  PCS_DISPATCH(p->dtype, pcs::gate_norm_add_kernel<T><<<p->n_rows, 256, smem, st>>>(*p));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
+
+PCS_API int pcs_xielu(const void* z, int64_t z_stride, void* out, int64_t out_stride, const void* a, int n_rows, int width,
+                      int dtype, void* stream) {
+  if (n_rows == 0) return PCS_OK;
+  PCS_REQUIRE(z && out && a && n_rows > 0 && width > 0, "pcs_xielu: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(n_rows, (width + 255) / 256 > 64 ? 64 : (width + 255) / 256);
+  PCS_DISPATCH(dtype, pcs::xielu_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(z), z_stride, static_cast<T*>(out), out_stride,
+                                                                 static_cast<const T*>(a), width));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}

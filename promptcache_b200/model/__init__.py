@@ -195,5 +195,60 @@ class Mpt(LanguageModel):
         return c.n_layers, c.n_heads, c.d_model // c.n_heads
 
 
-__all__ = ["LanguageModel", "Llama2", "CodeLlama", "Falcon", "Mpt", "FormatConversation",
+class Mutolix(LanguageModel):
+    """Adapter of the Mutolix design (model/mutolix.py) for the generation engine.  Its recurrent layers carry a state
+    that cannot be cut at module boundaries and spliced, so it is served without a segment cache: pass `cache=None` to
+    `GenerationEngine.generate`, or batch requests with `BatchEngine`."""
+
+    def __init__(self, name: str, model=None, tokenizer=None, **kwargs):
+        from .mutolix import MutolixForCausalLM
+        if model is None:
+            model = MutolixForCausalLM.from_pretrained(name, **kwargs)
+        if tokenizer is None:
+            from ..synthetic import IdTokenizer
+            tokenizer = IdTokenizer(model.vocab_size)
+        super().__init__(name, model, tokenizer, [tokenizer.eos_token_id], [])
+
+    def get_formatter(self) -> Callable[[str], str]:
+        return lambda prompt: prompt
+
+    def get_cache_shape(self) -> Tuple[int, int, int]:
+        raise NotImplementedError("Mutolix keeps recurrent state next to K/V rows: there is no per-module K/V to cache and splice")
+
+
+# config.json "architecture" (or transformers' "architectures"/"model_type") -> loader of the bare model
+MODEL_REGISTRY = {
+    "Mutolix": lambda path, **kw: _mutolix(path, **kw),
+    "LlamaForCausalLM": lambda path, dtype=None, **kw: LlamaForCausalLM.from_pretrained(path, **kw),
+    "FalconForCausalLM": lambda path, dtype=None, **kw: _lazy("falcon", "FalconForCausalLM").from_pretrained(path, **kw),
+    "MptForCausalLM": lambda path, dtype=None, **kw: _lazy("mpt", "MptForCausalLM").from_pretrained(path, **kw),
+}
+
+
+def _lazy(module: str, name: str):
+    import importlib
+    return getattr(importlib.import_module(f"{__name__}.{module}"), name)
+
+
+def _mutolix(path, **kw):
+    return _lazy("mutolix", "MutolixForCausalLM").from_pretrained(path, **kw)
+
+
+def load_model(path: str, device="cuda", dtype=None, **kwargs):
+    """Build the model a folder's config.json names: "architecture" (this package's own designs) or the first entry of
+    transformers' "architectures"."""
+    import json
+    import os
+    with open(os.path.join(path, "config.json")) as fh:
+        cfg = json.load(fh)
+    arch = cfg.get("architecture") or (cfg.get("architectures") or [None])[0]
+    loader = MODEL_REGISTRY.get(arch)
+    if loader is None:
+        raise ValueError(f"{path}: config.json names architecture {arch!r}; known: {sorted(MODEL_REGISTRY)}")
+    if dtype is not None:
+        kwargs["dtype"] = dtype
+    return loader(path, device=device, **kwargs)
+
+
+__all__ = ["LanguageModel", "Mutolix", "MODEL_REGISTRY", "load_model", "Llama2", "CodeLlama", "Falcon", "Mpt", "FormatConversation",
            "FormatLlama2Conversation", "LlamaForCausalLM", "LlamaConfigLite"]
