@@ -116,8 +116,12 @@ typedef struct pcs_attn_params {
   const int32_t* seq_off;
   int32_t n_tokens, n_seqs, max_len, dtype;   /* max_len: host upper bound of the new tokens of one entry */
   int32_t impl;             /* 0 = automatic, 1 = the plain kernel */
-  int32_t reserved;
+  int32_t max_keys;         /* host upper bound of the keys one token sees (sizes the split of the keys); 0: one split */
+  float* workspace;         /* fp32 scratch of pcs_attn_workspace_floats() elements, or NULL (one split) */
+  int64_t workspace_floats;
 } pcs_attn_params;
+/* scratch the key split of pcs_attn needs for n_tokens tokens */
+int64_t pcs_attn_workspace_floats(int n_tokens, int n_heads, int vdim);
 int pcs_attn(const pcs_attn_params* p, void* stream);
 
 /* ig = cap * tanh((w_i h + b_i) / cap);  fg = logsigmoid(cap * tanh((w_f h + b_f) / cap))    (fp32 [n_tokens, heads]) */
@@ -145,6 +149,9 @@ typedef struct pcs_mlstm_params {
   int32_t n_seqs, dtype;
   int32_t max_len;          /* host upper bound of the new tokens of one entry */
   int32_t impl;             /* 0 = automatic, 1 = the token-by-token kernel */
+  float* o_raw;             /* fp32 scratch of n_tokens*heads*vdim + n_seqs*heads*(dim+1) elements: the recurrence's result before
+                               the per-head norm, and the new n / m of every entry until they are committed */
+  int32_t n_tokens, reserved;
 } pcs_mlstm_params;
 int pcs_mlstm_scan(const pcs_mlstm_params* p, void* stream);
 

@@ -16,7 +16,7 @@ from ._native import NativeError, note_replayed_launches  # noqa: F401  (one err
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libpromptcache_b200_seq.so")
 PCS_BF16, PCS_F32 = 0, 1
-EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu",
+EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_attn_workspace_floats", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu",
            "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan")
 
 
@@ -44,7 +44,7 @@ class pcs_attn_params(C.Structure):
                 ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p),
                 ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
                 ("n_tokens", C.c_int32), ("n_seqs", C.c_int32), ("max_len", C.c_int32), ("dtype", C.c_int32),
-                ("impl", C.c_int32), ("reserved", C.c_int32)]
+                ("impl", C.c_int32), ("max_keys", C.c_int32), ("workspace", C.c_void_p), ("workspace_floats", C.c_int64)]
 
 
 class pcs_mlstm_params(C.Structure):
@@ -54,7 +54,8 @@ class pcs_mlstm_params(C.Structure):
                 ("s_pool", C.c_void_p), ("n_pool", C.c_void_p), ("m_pool", C.c_void_p),
                 ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("q_scale", C.c_float), ("eps", C.c_float),
                 ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p), ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
-                ("n_seqs", C.c_int32), ("dtype", C.c_int32), ("max_len", C.c_int32), ("impl", C.c_int32)]
+                ("n_seqs", C.c_int32), ("dtype", C.c_int32), ("max_len", C.c_int32), ("impl", C.c_int32),
+                ("o_raw", C.c_void_p), ("n_tokens", C.c_int32), ("reserved", C.c_int32)]
 
 
 _lib: Optional[C.CDLL] = None
@@ -85,7 +86,9 @@ def load() -> C.CDLL:
     lib.pcs_mlstm_gates.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
     lib.pcs_mlstm_scan.argtypes = [C.POINTER(pcs_mlstm_params), C.c_void_p]
-    for name in EXPORTS[3:]:
+    lib.pcs_attn_workspace_floats.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.pcs_attn_workspace_floats.restype = C.c_int64
+    for name in EXPORTS[4:]:
         getattr(lib, name).restype = C.c_int
     _lib = lib
     return lib
@@ -221,8 +224,11 @@ def qk_prep(qkv: torch.Tensor, offs, q_norm_w, k_norm_w, eps: float, n_heads: in
 
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float,
-              r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: bool, batch: Batch, impl: int = 0) -> None:
-    """q [T, H*dim], out [T, H*vdim]; causal over each entry's own slot rows; r1 / r2 float32 [H] or None."""
+              r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: bool, batch: Batch, impl: int = 0,
+              max_keys: int = 0, workspace: Optional[torch.Tensor] = None) -> None:
+    """q [T, H*dim], out [T, H*vdim]; causal over each entry's own slot rows; r1 / r2 float32 [H] or None.  With a float32
+    `workspace` (attn_workspace) and `max_keys` (upper bound of the keys a token sees) few tokens over many keys are run
+    as several splits of the keys that a second launch merges."""
     _cuda(q, k_pool, v_pool, out, r1, r2)
     dt = q.dtype
     if not (q.is_contiguous() and out.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous()) or out.dtype != dt \
@@ -238,7 +244,15 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
     p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
     p.seq_pos0, p.seq_len, p.seq_off = batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(), batch.seq_off.data_ptr()
     p.n_tokens, p.n_seqs, p.max_len, p.dtype, p.impl = batch.n_tokens, batch.n_seqs, batch.max_len, dtype_code(dt), impl
+    if workspace is not None:
+        if workspace.dtype != torch.float32 or not workspace.is_cuda or not workspace.is_contiguous():
+            raise NativeError("attention: the workspace must be a contiguous CUDA float32 tensor")
+        p.max_keys, p.workspace, p.workspace_floats = int(max_keys), workspace.data_ptr(), workspace.numel()
     _check(load().pcs_attn(C.byref(p), _stream()), "pcs_attn")
+
+
+def attn_workspace(n_tokens: int, n_heads: int, vdim: int, device) -> torch.Tensor:
+    return torch.empty(int(load().pcs_attn_workspace_floats(n_tokens, n_heads, vdim)), dtype=torch.float32, device=device)
 
 
 def mlstm_gates(h: torch.Tensor, w_i: torch.Tensor, w_f: torch.Tensor, b_i: torch.Tensor, b_f: torch.Tensor, ig: torch.Tensor,
@@ -273,4 +287,7 @@ def mlstm_scan(proj: torch.Tensor, offs, ig: torch.Tensor, fg: torch.Tensor, nor
     p.seq_slot, p.seq_pos0, p.seq_len, p.seq_off = (batch.seq_slot.data_ptr(), batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(),
                                                     batch.seq_off.data_ptr())
     p.n_seqs, p.dtype, p.max_len, p.impl = batch.n_seqs, dtype_code(dt), batch.max_len, impl
+    # scratch: the recurrence's raw result per token, and the new n / m per entry until the commit launch stores them
+    o_raw = torch.empty(batch.n_tokens * p.heads * p.vdim + batch.n_seqs * p.heads * (p.dim + 1), dtype=torch.float32, device=proj.device)
+    p.o_raw, p.n_tokens = o_raw.data_ptr(), batch.n_tokens
     _check(load().pcs_mlstm_scan(C.byref(p), _stream()), "pcs_mlstm_scan")

@@ -3,7 +3,7 @@
 // pcs_qk_prep   one block per token: RMS norm over the WHOLE query projection (all heads at once) and over the whole key
 //               projection, query temperature from the token's position, value mixing with the rows an earlier layer
 //               appended for the same token, K / V rows written behind the slot's cached rows.
-// pcs_attn      one block per (token, head): keys in tiles of 128, one key per thread for the score, online softmax in
+// pcs_attn      one block per (token, head, split of the keys): keys in tiles of 128, one key per thread for the score, online softmax in
 //               32-bit, then one value column per thread.  Scores, weights and the accumulator are 32-bit in both types.
 //               A sink is one more term exp(0 - m) of the denominator that has no value: the running maximum starts at 0
 //               and the running sum at 1 instead of (-inf, 0).
@@ -92,15 +92,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
   for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
   const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
-  float m = p.sink ? 0.f : -INFINITY, l = p.sink ? 1.f : 0.f;
+  // keys are cut into gridDim.z splits of whole tiles; the sink belongs to split 0
+  const int n_keys = pos + 1, S = gridDim.z, sp = blockIdx.z;
+  const int chunk = ((n_keys + S - 1) / S + kAttnThreads - 1) / kAttnThreads * kAttnThreads;
+  const int k_begin = sp * chunk, k_end = min(n_keys, k_begin + chunk);
+  const bool sink_here = p.sink && sp == 0;
+  float m = sink_here ? 0.f : -INFINITY, l = sink_here ? 1.f : 0.f;
   float acc[kAttnMaxVPT] = {0.f, 0.f, 0.f, 0.f};
   const bool vec = (D % Vec<T>::n) == 0;
   __syncthreads();
-  const int n_keys = pos + 1;
-  for (int j0 = 0; j0 < n_keys; j0 += kAttnThreads) {
+  for (int j0 = k_begin; j0 < k_end; j0 += kAttnThreads) {
     const int j = j0 + tid;
     float s = -INFINITY;
-    if (j < n_keys) {
+    if (j < k_end) {
       const T* kr = K + static_cast<long long>(j) * D;
       float a = 0.f;
       if (vec) {
@@ -119,12 +123,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
     const float tmax = block_max(s, red);
     const float m_new = fmaxf(m, tmax);
     const float f = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    const float w = (j < n_keys) ? expf(s - m_new) : 0.f;
+    const float w = (j < k_end) ? expf(s - m_new) : 0.f;
     ws[tid] = w;
     const float tsum = block_sum(w, red);  // its barriers also publish ws
     l = l * f + tsum;
     m = m_new;
-    const int nt = min(kAttnThreads, n_keys - j0);
+    const int nt = min(kAttnThreads, k_end - j0);
 #pragma unroll
     for (int u = 0; u < kAttnMaxVPT; ++u) {
       const int c = tid + u * kAttnThreads;
@@ -137,6 +141,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
     }
     __syncthreads();  // ws is rewritten by the next tile
   }
+  if (S > 1) {  // partial (m, l, acc) of this split; attn_combine_kernel merges them
+    float* part = p.workspace + ((static_cast<long long>(t) * p.n_heads + h) * S + sp) * (V + 2);
+    if (tid == 0) { part[0] = m; part[1] = l; }
+#pragma unroll
+    for (int u = 0; u < kAttnMaxVPT; ++u) {
+      const int c = tid + u * kAttnThreads;
+      if (c < V) part[2 + c] = acc[u];
+    }
+    return;
+  }
   T* o = static_cast<T*>(p.out) + (static_cast<long long>(t) * p.n_heads + h) * V;
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -146,7 +160,37 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads) attn_combine_kernel(const pcs_attn_params p, int S) {
+  const int t = blockIdx.x, h = blockIdx.y, V = p.vdim;
+  const float* part = p.workspace + (static_cast<long long>(t) * p.n_heads + h) * S * (V + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, part[s * (V + 2)]);
+  float L = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float ms = part[s * (V + 2)];
+    if (ms != -INFINITY) L += part[s * (V + 2) + 1] * expf(ms - M);
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  T* o = static_cast<T*>(p.out) + (static_cast<long long>(t) * p.n_heads + h) * V;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float ms = part[s * (V + 2)];
+      if (ms != -INFINITY) a = fmaf(part[s * (V + 2) + 2 + c], expf(ms - M), a);
+    }
+    stf(o + c, a * inv);
+  }
+}
+
+constexpr int kAttnMaxSplits = 32;
+
 }  // namespace pcs
+
+PCS_API int64_t pcs_attn_workspace_floats(int n_tokens, int n_heads, int vdim) {
+  if (n_tokens <= 0 || n_heads <= 0 || vdim <= 0) return 0;
+  return static_cast<int64_t>(n_tokens) * n_heads * pcs::kAttnMaxSplits * (vdim + 2);
+}
 
 PCS_API int pcs_qk_prep(const pcs_qkprep_params* p, void* stream) {
   PCS_REQUIRE(p, "pcs_qk_prep: null params");
@@ -184,9 +228,26 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
   }
   const size_t smem = static_cast<size_t>(p->dim + pcs::kAttnThreads) * sizeof(float);
   PCS_REQUIRE(smem <= 48 * 1024, "pcs_attn: dim %d exceeds the shared-memory query row", p->dim);
-  dim3 grid(p->n_tokens, p->n_heads);
+  // few tokens over many keys (decoding): the keys are split so that the launch fills the GPU; each split has >= 256 keys
+  int splits = 1;
+  if (p->workspace != nullptr && p->max_keys > 512) {
+    const long long blocks = static_cast<long long>(p->n_tokens) * p->n_heads;
+    const int want = static_cast<int>((2 * 148 + blocks - 1) / blocks);
+    splits = p->max_keys / 256;
+    if (splits > want) splits = want;
+    if (splits > pcs::kAttnMaxSplits) splits = pcs::kAttnMaxSplits;
+    if (splits < 1) splits = 1;
+    PCS_REQUIRE(splits == 1 || p->workspace_floats >= static_cast<long long>(p->n_tokens) * p->n_heads * splits * (p->vdim + 2),
+                "pcs_attn: workspace too small for %d splits", splits);
+  }
+  dim3 grid(p->n_tokens, p->n_heads, splits);
   PCS_DISPATCH(p->dtype, pcs::attn_plain_kernel<T><<<grid, pcs::kAttnThreads, smem, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
+  if (splits > 1) {
+    PCS_DISPATCH(p->dtype, pcs::attn_combine_kernel<T><<<dim3(p->n_tokens, p->n_heads), pcs::kAttnThreads, 0, st>>>(*p, splits));
+    PCS_CHECK_CUDA(cudaGetLastError());
+    pcs::count_launch();
+  }
   return PCS_OK;
 }

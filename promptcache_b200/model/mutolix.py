@@ -181,7 +181,11 @@ class MutolixForCausalLM(SlotPoolCausalLM):
                 vf = self.pool.layers[blk["mix_from"]]["v"] if blk["mix_from"] is not None else None
                 nsq.qk_prep(proj, blk["offs"], blk["q_norm"], blk["k_norm"], eps, H, blk["kv_heads"], blk["dim"], V, blk["temp_coef"],
                             blk["temp_every"], q, st["k"], st["v"], vf, blk["lam"], batch)
-                nsq.attention(q, st["k"], st["v"], mixed, H, blk["scale"], blk["r1"], blk["r2"], True, batch, impl=self.attn_impl)
+                # few tokens (decoding): the keys are split over more blocks; the bound is the pool's capacity, so that a
+                # replayed graph stays valid while the sequences grow
+                ws = nsq.attn_workspace(T, H, V, dev) if T <= 16 else None
+                nsq.attention(q, st["k"], st["v"], mixed, H, blk["scale"], blk["r1"], blk["r2"], True, batch, impl=self.attn_impl,
+                              max_keys=self.pool.cap, workspace=ws)
             y = F.linear(mixed, blk["w_o"])
             gate = proj[:, blk["rg_off"]:] if blk["gated1"] else None
             has_ff = blk["ff"] > 0

@@ -103,7 +103,7 @@ def test_embed_scale(nsq):
     close(out, table[ids.cpu()] * 0.375, 1e-7, "embedding")
 
 
-def _attn_case(nsq, H, G, D, V, lens_pos0, scale, bias=True, sink=True, dtype=F32, seed=0, boost=None, cap=None):
+def _attn_case(nsq, H, G, D, V, lens_pos0, scale, bias=True, sink=True, dtype=F32, seed=0, boost=None, cap=None, split=False):
     """Run qk-free attention over hand-made pools: entry b holds pos0[b] rows and brings lens[b] new tokens."""
     g = torch.Generator().manual_seed(seed)
     rnd = lambda *s: torch.randn(*s, generator=g, dtype=O.F64)
@@ -129,7 +129,9 @@ def _attn_case(nsq, H, G, D, V, lens_pos0, scale, bias=True, sink=True, dtype=F3
     batch = nsq.Batch(slots, [p for _, p in lens_pos0], [n for n, _ in lens_pos0], torch.device(DEV))
     q = torch.cat(qs).reshape(-1, H * D)
     out = torch.empty(q.shape[0], H * V, device=DEV, dtype=dtype)
-    nsq.attention(dev(q, dtype), dev(kp, dtype), dev(vp, dtype), out, H, scale, dev(r1) if bias else None, dev(r2) if bias else None, sink, batch)
+    extra = dict(max_keys=cap, workspace=nsq.attn_workspace(q.shape[0], H, V, DEV)) if split else {}
+    nsq.attention(dev(q, dtype), dev(kp, dtype), dev(vp, dtype), out, H, scale, dev(r1) if bias else None, dev(r2) if bias else None, sink, batch,
+                  **extra)
     return out, torch.cat(want)
 
 
@@ -151,6 +153,16 @@ def test_attention_key_tile_edges_and_far_keys(nsq):
         close(out, want, 1e-5, f"far key {far}")
         out, want = _attn_case(nsq, 4, 2, 16, 8, [(701, 0)], 0.5, bias=False, boost=(far, 4.0), seed=far)
         close(out[-1:], want[-1:], 1e-5, f"far key {far} in a prompt")
+
+
+def test_attention_split_keys(nsq):
+    """Decoding over many keys runs as several splits of the keys (whole tiles each) merged by a second launch: sequences of
+    unequal lengths in one launch, one of them shorter than a split, with and without the sink and the bias."""
+    for bias, sink in ((True, True), (False, False)):
+        out, want = _attn_case(nsq, 4, 2, 16, 24, [(1, 2047), (1, 3), (1, 1300), (1, 0)], 0.25, bias, sink, cap=2048, split=True)
+        close(out, want, 5e-6, f"split keys bias={bias} sink={sink}")
+    out, want = _attn_case(nsq, 2, 1, 16, 8, [(1, 1500)], 0.5, bias=False, boost=(2, 4.0), cap=2048, split=True)
+    close(out, want, 1e-5, "far key in the first split")
 
 
 def test_attention_sink_matters(nsq):
@@ -188,7 +200,7 @@ def test_qk_prep_norm_temperature_mixing_append(nsq, every):
     assert float(kp[0].abs().max()) == 0 and float(kp[slot, :, :pos0].abs().max()) == 0 and float(kp[slot, :, pos0 + T:].abs().max()) == 0
 
 
-@pytest.mark.parametrize("H,D,V", [(2, 8, 16), (1, 16, 8), (3, 12, 20), (2, 64, 128)])
+@pytest.mark.parametrize("H,D,V", [(2, 8, 16), (1, 16, 8), (3, 12, 20), (2, 64, 128), (1, 16, 160)])
 def test_mlstm_gates_and_scan(nsq, H, D, V):
     """The recurrence in one piece, in portions through the pooled state, and as single tokens; large gate values reach
     the cap and the running maximum."""
