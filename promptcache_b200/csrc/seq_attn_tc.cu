@@ -1,10 +1,226 @@
-// Tensor-core attention over the slot pool (bfloat16 prefill).  Placeholder dispatch: declines every shape, so the plain
-// kernel runs.
+// Tensor-core attention over the slot pool for prompts (bfloat16 storage).
+//
+// One block = 64 consecutive new tokens of one sequence and one head, 4 warps of 16 query rows each; keys in tiles of 64.
+// Q, K and V tiles are staged in shared memory (rows padded by 16 bytes), fragments come from ldmatrix, products are
+// m16n8k16 bfloat16 tensor-core operations with 32-bit accumulators held in registers:
+//     S = Q K^T           32-bit scores; scale, distance bias r1 ln(1 + r2 (i - j)) and the causal mask applied per score
+//     online softmax      running maximum / sum per query row in 32-bit; a sink starts them at (0, 1) instead of (-inf, 0)
+//     O += P V            the 32-bit weights enter the tensor cores as TWO bfloat16 operands, P = hi + lo with
+//                         hi = bf16(P), lo = bf16(P - hi), so that the product keeps ~16 bits of every weight instead of 8
+// Key / value widths are padded in shared memory to 64, 128 or 256 (zero fill); every width that is a multiple of 8 up to
+// 256 is served.  Other types and shapes fall to the plain kernel (seq_attn.cu).
 #include "seq_common.cuh"
 
 namespace pcs {
-int launch_attn_tc(const pcs_attn_params&, cudaStream_t, bool* handled) {
-  *handled = false;
+
+namespace {
+
+constexpr int BM = 64, BN = 64, TC_THREADS = 128, PAD = 8;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// P = hi + lo in bfloat16: returns the packed hi pair, `lo_pair` gets the packed remainders
+__device__ __forceinline__ uint32_t split_pair(float p0, float p1, uint32_t& lo_pair) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
+  lo_pair = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+  const __nv_bfloat162 v = __halves2bfloat162(h0, h1);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// rows [row0, row0 + 64) x `width` of a [*, src_stride] bfloat16 matrix into a [64][WP + PAD] tile; rows >= n_rows and
+// columns >= width are zero
+template <int WP>
+__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat16* src, long long src_stride, int row0, int n_rows,
+                                          int width) {
+  constexpr int CH = WP / 8;
+  for (int e = threadIdx.x; e < BM * CH; e += TC_THREADS) {
+    const int r = e / CH, c = (e - r * CH) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row0 + r < n_rows && c < width) v = *reinterpret_cast<const uint4*>(src + static_cast<long long>(row0 + r) * src_stride + c);
+    *reinterpret_cast<uint4*>(dst + r * (WP + PAD) + c) = v;
+  }
+}
+
+template <int DP, int VP>
+__global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* Ks = Qs + BM * (DP + PAD);
+  __nv_bfloat16* Vs = Ks + BN * (DP + PAD);
+  const int b = blockIdx.y, h = blockIdx.z, q0 = blockIdx.x * BM;
+  const int len = p.seq_len[b];
+  if (q0 >= len) return;
+  const int pos0 = p.seq_pos0[b], off = p.seq_off[b], slot = p.seq_slot[b];
+  const int g = h / (p.n_heads / p.n_kv_heads), D = p.dim, V = p.vdim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 2, qd = lane & 3;
+  const __nv_bfloat16* Kg = static_cast<const __nv_bfloat16*>(p.k_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * D;
+  const __nv_bfloat16* Vg = static_cast<const __nv_bfloat16*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
+  const __nv_bfloat16* Qg = static_cast<const __nv_bfloat16*>(p.q) + static_cast<long long>(off) * p.n_heads * D + h * D;
+  load_tile<DP>(Qs, Qg, static_cast<long long>(p.n_heads) * D, q0, len, D);
+  const int total_keys = pos0 + len;
+  const int n_keys = min(total_keys, pos0 + q0 + BM);  // the last row of this tile sees keys below this bound
+  const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
+  const bool bias = p.bias_r1 != nullptr;
+  // this thread's two query rows (grp, grp + 8 of the warp's 16) and their positions
+  const int row_a = warp * 16 + grp, row_b = row_a + 8;
+  const int pq_a = pos0 + q0 + row_a, pq_b = pos0 + q0 + row_b;
+  float m_a = p.sink ? 0.f : -INFINITY, m_b = m_a;
+  float l_a = (p.sink && qd == 0) ? 1.f : 0.f, l_b = l_a;  // per-thread share of the row sums; the sink's 1 sits in one lane
+  float o[VP / 8][4];
+#pragma unroll
+  for (int i = 0; i < VP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const uint32_t q_base = static_cast<uint32_t>(__cvta_generic_to_shared(Qs)) +
+                          ((warp * 16 + (lane & 15)) * (DP + PAD) + (lane >> 4) * 8) * 2;
+  const uint32_t k_base = static_cast<uint32_t>(__cvta_generic_to_shared(Ks)) + (((lane & 7)) * (DP + PAD) + (lane >> 3) * 8) * 2;
+  const uint32_t v_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs)) + ((lane & 15) * (VP + PAD) + (lane >> 4) * 8) * 2;
+
+  for (int k0 = 0; k0 < n_keys; k0 += BN) {
+    __syncthreads();  // the previous tile's fragments have been read (and Q is complete on the first pass)
+    load_tile<DP>(Ks, Kg, D, k0, total_keys, D);
+    load_tile<VP>(Vs, Vg, V, k0, total_keys, V);
+    __syncthreads();
+    // ---- S = Q K^T: 16 rows x 64 keys per warp ----
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; kk += 2) {
+      uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+      ldsm_x4(q_base + kk * 32, a0, a1, a2, a3);
+      ldsm_x4(q_base + (kk + 1) * 32, c0, c1, c2, c3);
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt) {
+        uint32_t b0, b1, b2, b3;  // keys nt*8.., dims kk*16.. (b0,b1) and (kk+1)*16.. (b2,b3)
+        ldsm_x4(k_base + (nt * 8 * (DP + PAD) + kk * 16) * 2, b0, b1, b2, b3);
+        mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[nt], c0, c1, c2, c3, b2, b3);
+      }
+    }
+    // ---- scale, distance bias, causal mask; row maxima ----
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int pk = k0 + nt * 8 + qd * 2 + (e & 1);
+        const int pq = (e < 2) ? pq_a : pq_b;
+        float v = s[nt][e] * p.scale;
+        if (pk > pq || pk >= total_keys) {
+          v = -INFINITY;
+        } else if (bias) {
+          v -= r1 * __logf(fmaf(r2, static_cast<float>(pq - pk), 1.f));
+        }
+        s[nt][e] = v;
+        if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+      }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float f_a = (m_a == -INFINITY) ? 0.f : __expf(m_a - mn_a), f_b = (m_b == -INFINITY) ? 0.f : __expf(m_b - mn_b);
+    m_a = mn_a;
+    m_b = mn_b;
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mn = (e < 2) ? mn_a : mn_b;
+        const float w = (s[nt][e] == -INFINITY) ? 0.f : __expf(s[nt][e] - mn);
+        s[nt][e] = w;
+        if (e < 2) sum_a += w; else sum_b += w;
+      }
+    }
+    l_a = l_a * f_a + sum_a;
+    l_b = l_b * f_b + sum_b;
+#pragma unroll
+    for (int i = 0; i < VP / 8; ++i) {
+      o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b;
+    }
+    // ---- O += P V, P as hi + lo ----
+#pragma unroll
+    for (int j = 0; j < BN / 16; ++j) {
+      uint32_t lo0, lo1, lo2, lo3;
+      const uint32_t hi0 = split_pair(s[2 * j][0], s[2 * j][1], lo0);
+      const uint32_t hi1 = split_pair(s[2 * j][2], s[2 * j][3], lo1);
+      const uint32_t hi2 = split_pair(s[2 * j + 1][0], s[2 * j + 1][1], lo2);
+      const uint32_t hi3 = split_pair(s[2 * j + 1][2], s[2 * j + 1][3], lo3);
+#pragma unroll
+      for (int vn = 0; vn < VP / 8; vn += 2) {
+        uint32_t b0, b1, b2, b3;  // keys j*16.., value columns vn*8.. (b0,b1) and (vn+1)*8.. (b2,b3)
+        ldsm_x4_t(v_base + (j * 16 * (VP + PAD) + vn * 8) * 2, b0, b1, b2, b3);
+        mma_bf16(o[vn], hi0, hi1, hi2, hi3, b0, b1);
+        mma_bf16(o[vn], lo0, lo1, lo2, lo3, b0, b1);
+        mma_bf16(o[vn + 1], hi0, hi1, hi2, hi3, b2, b3);
+        mma_bf16(o[vn + 1], lo0, lo1, lo2, lo3, b2, b3);
+      }
+    }
+  }
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(off) * p.n_heads * V + h * V;
+#pragma unroll
+  for (int vn = 0; vn < VP / 8; ++vn) {
+    const int c = vn * 8 + qd * 2;
+    if (c < V) {
+      if (q0 + row_a < len)
+        *reinterpret_cast<uint32_t*>(out + static_cast<long long>(q0 + row_a) * p.n_heads * V + c) = pack_bf16(o[vn][0] * inv_a, o[vn][1] * inv_a);
+      if (q0 + row_b < len)
+        *reinterpret_cast<uint32_t*>(out + static_cast<long long>(q0 + row_b) * p.n_heads * V + c) = pack_bf16(o[vn][2] * inv_b, o[vn][3] * inv_b);
+    }
+  }
+}
+
+template <int DP, int VP>
+int launch(const pcs_attn_params& p, cudaStream_t st) {
+  const size_t smem = (static_cast<size_t>(BM + BN) * (DP + PAD) + static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    configured = true;
+  }
+  dim3 grid((p.max_len + BM - 1) / BM, p.n_seqs, p.n_heads);
+  attn_tc_kernel<DP, VP><<<grid, TC_THREADS, smem, st>>>(p);
+  PCS_CHECK_CUDA(cudaGetLastError());
+  count_launch();
   return PCS_OK;
 }
+
+template <int DP>
+int launch_v(const pcs_attn_params& p, cudaStream_t st) {
+  if (p.vdim <= 64) return launch<DP, 64>(p, st);
+  if (p.vdim <= 128) return launch<DP, 128>(p, st);
+  return launch<DP, 256>(p, st);
+}
+
+}  // namespace
+
+int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled) {
+  *handled = false;
+  if (p.dtype != PCS_BF16 || p.max_len < 16 || p.dim % 8 != 0 || p.vdim % 8 != 0 || p.dim > 256 || p.vdim > 256) return PCS_OK;
+  if (p.n_seqs > 65535 || p.n_heads > 65535 || !p.seq_pos0 || !p.seq_len || !p.seq_off) return PCS_OK;
+  *handled = true;
+  if (p.dim <= 64) return launch_v<64>(p, st);
+  if (p.dim <= 128) return launch_v<128>(p, st);
+  return launch_v<256>(p, st);
+}
+
 }  // namespace pcs

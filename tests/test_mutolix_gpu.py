@@ -103,7 +103,7 @@ def test_embed_scale(nsq):
     close(out, table[ids.cpu()] * 0.375, 1e-7, "embedding")
 
 
-def _attn_case(nsq, H, G, D, V, lens_pos0, scale, bias=True, sink=True, dtype=F32, seed=0, boost=None, cap=None, split=False):
+def _attn_case(nsq, H, G, D, V, lens_pos0, scale, bias=True, sink=True, dtype=F32, seed=0, boost=None, cap=None, split=False, impl=0):
     """Run qk-free attention over hand-made pools: entry b holds pos0[b] rows and brings lens[b] new tokens."""
     g = torch.Generator().manual_seed(seed)
     rnd = lambda *s: torch.randn(*s, generator=g, dtype=O.F64)
@@ -131,7 +131,7 @@ def _attn_case(nsq, H, G, D, V, lens_pos0, scale, bias=True, sink=True, dtype=F3
     out = torch.empty(q.shape[0], H * V, device=DEV, dtype=dtype)
     extra = dict(max_keys=cap, workspace=nsq.attn_workspace(q.shape[0], H, V, DEV)) if split else {}
     nsq.attention(dev(q, dtype), dev(kp, dtype), dev(vp, dtype), out, H, scale, dev(r1) if bias else None, dev(r2) if bias else None, sink, batch,
-                  **extra)
+                  impl=impl, **extra)
     return out, torch.cat(want)
 
 
@@ -176,6 +176,21 @@ def test_attention_sink_matters(nsq):
 def test_attention_bf16_inputs(nsq):
     out, want = _attn_case(nsq, 8, 2, 64, 32, [(200, 0), (1, 333), (40, 100)], 0.125, dtype=BF16)
     close(out, want, 1e-2, "bf16 attention")      # the output is rounded to bfloat16; scores and weights are not
+
+
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 96, 32), (2, 2, 64, 64), (4, 1, 128, 128), (2, 1, 256, 256), (3, 3, 24, 40), (2, 1, 8, 200)])
+def test_attention_tensor_core_prompts(nsq, H, G, D, V):
+    """Prompts in bfloat16 run on the tensor-core kernel: portions that start inside a sequence, ends just inside and just
+    outside the 64-row and 64-key tiles, against the oracle and against the plain kernel on the same inputs."""
+    for case in ([(64, 0), (65, 63), (17, 0)], [(200, 0), (1, 333), (40, 100)], [(63, 1), (129, 127), (16, 48)]):
+        for bias, sink in ((True, True), (False, False)):
+            out, want = _attn_case(nsq, H, G, D, V, case, D ** -0.5, bias, sink, dtype=BF16, seed=D + V)
+            plain, _ = _attn_case(nsq, H, G, D, V, case, D ** -0.5, bias, sink, dtype=BF16, seed=D + V, impl=1)
+            close(out, want, 1e-2, f"tensor-core attention {case} bias={bias} sink={sink}")
+            close(out.float(), plain.float().cpu(), 1e-2, "tensor-core vs plain kernel")
+            assert float((out.float() - plain.float()).abs().mean()) < 1e-3 * float(plain.float().abs().mean())
+    out, want = _attn_case(nsq, H, G, D, V, [(701, 0)], 0.5, bias=False, dtype=BF16, boost=(3, 4.0), seed=1)
+    close(out[-1:], want[-1:], 1e-2, "far key in a prompt")
 
 
 @pytest.mark.parametrize("every", [0, 4])
