@@ -1,0 +1,230 @@
+"""Throughput of the slot-pool design (Mutolix) beside the closest prompt-cache model (Llama) at equal sizes: `bench.py
+--design mutolix`.  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
+step / forward, then every kernel of the new design alone against its roofline, next to the like kernel of the Llama path.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up iterations, a 256 MiB write between timed iterations (flushes the
+126 MB L2), median of the timed iterations.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+from typing import Callable, Dict, List
+
+import torch
+
+SIZES = {
+    # width, attention heads / kv heads / dim / vdim, recurrent heads / dim / vdim, ff, layers (pattern repeated), vocab
+    "w1024": dict(width=1024, H=8, G=2, D=128, V=128, mH=4, mD=128, mV=256, ff=4096, repeat=1, vocab=8192),
+    "w2048": dict(width=2048, H=16, G=4, D=128, V=128, mH=4, mD=256, mV=512, ff=8192, repeat=2, vocab=8192),
+}
+
+
+def mutolix_config(s: dict) -> dict:
+    attn = {"type": "attention", "mixer": {"heads": s["H"], "kv_heads": s["G"], "dim": s["D"], "vdim": s["V"], "scale": s["D"] ** -0.5,
+                                            "v_mix": True, "q_temp": {"coef": 0.3, "every": 256}}, "mlp": {"kind": "dense", "ff": s["ff"]}}
+    rec = {"type": "mlstm", "mixer": {"heads": s["mH"], "dim": s["mD"], "vdim": s["mV"], "gate_cap": 12.0}, "mlp": {"kind": "dense", "ff": s["ff"]}}
+    return {"architecture": "Mutolix", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": [rec, attn, attn, rec] * s["repeat"]}
+
+
+def random_tensors(cfg: dict, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random bfloat16 tensors with the checkpoint's names and shapes, made on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    W, t = cfg["width"], {}
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return (torch.randn(*shape, generator=g, device=device) * std + mean).to(torch.bfloat16)
+
+    lin = lambda o, i: rnd(o, i, std=i ** -0.5)
+    t["embed"], t["final.norm"], t["head"] = rnd(cfg["vocab"], W), rnd(W, std=0.05, mean=1.0), lin(cfg["vocab"], W)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            t[p + n] = rnd(W, std=0.05, mean=1.0)
+        for n in ("ls1", "ls2"):
+            t[p + n] = rnd(W, std=0.1, mean=0.5)
+        for n in ("rg1", "rg2"):
+            t[p + n], t[p + n + ".b"] = lin(W, W), rnd(W, std=0.3)
+        if layer["type"] == "mlstm":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = lin(H * D, W), lin(H * D, W), lin(H * V, W), lin(H * V, W)
+            t[p + "mix.o"], t[p + "mix.norm"] = lin(W, H * V), rnd(H * V, std=0.05, mean=1.0)
+            t[p + "mix.i"], t[p + "mix.i.b"], t[p + "mix.f"], t[p + "mix.f.b"] = lin(H, W), rnd(H), lin(H, W), rnd(H, mean=3.0)
+        else:
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * V)):
+                t[p + "mix." + n], t[p + "mix." + n + ".b"] = lin(rows, W), rnd(rows, std=0.1)
+            t[p + "mix.q.norm"], t[p + "mix.k.norm"] = rnd(H * D, std=0.1, mean=1.0), rnd(G * D, std=0.1, mean=1.0)
+            t[p + "mix.vmix"], t[p + "mix.o"] = rnd(1, std=0.05, mean=0.4).reshape(()), lin(W, H * V)
+            t[p + "mix.r1"], t[p + "mix.r2"] = rnd(H, std=0.05, mean=0.5).abs(), rnd(H, std=0.1, mean=0.5).abs()
+        ff = layer["mlp"]["ff"]
+        t[p + "mlp.up"], t[p + "mlp.down"], t[p + "mlp.act"] = lin(ff, W), lin(W, ff), rnd(2, std=0.3)
+    return t
+
+
+class Timer:
+    def __init__(self, device):
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def __call__(self, fn: Callable[[], None], steps: int = 7, warmup: int = 3, setup: Callable[[], None] = None) -> float:
+        """Median milliseconds of fn()."""
+        ms = []
+        for i in range(warmup + steps):
+            if setup is not None:
+                setup()
+            self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                ms.append(a.elapsed_time(b))
+        return statistics.median(ms)
+
+
+def model_block(name: str, s: dict, dev, timer: Timer, prompt: int, batch: int, ctx: int) -> dict:
+    from .model.llama2 import LlamaConfigLite, LlamaForCausalLM
+    from .model.mutolix import MutolixConfig, MutolixForCausalLM
+    cfg = mutolix_config(s)
+    m = MutolixForCausalLM(MutolixConfig(cfg), random_tensors(cfg, dev), device=dev, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    toks = lambda n: torch.randint(0, s["vocab"], (n,), generator=g).tolist()
+    out = {"layers": len(cfg["layers"]), "width": s["width"]}
+    # ---- the new design: prefill of one prompt, of `batch` prompts, decode of 1 and of `batch` sequences at `ctx` tokens ----
+    seqs: List = []
+
+    def fresh(n):
+        for q in seqs:
+            q.free()
+        seqs[:] = [m.new_sequence() for _ in range(n)]
+
+    p1, pb = toks(prompt), [toks(prompt // 2) for _ in range(batch)]
+    ms = timer(lambda: m.step([(seqs[0], p1)]), setup=lambda: fresh(1), steps=5)
+    out["prefill_1x%d_tok_s" % prompt] = round(prompt / ms * 1e3)
+    ms = timer(lambda: m.step([(q, t) for q, t in zip(seqs, pb)]), setup=lambda: fresh(batch), steps=5)
+    out["prefill_%dx%d_tok_s" % (batch, prompt // 2)] = round(batch * (prompt // 2) / ms * 1e3)
+    for nb in (1, batch):
+        fresh(nb)
+        m.step([(q, toks(ctx)) for q in seqs])
+        for _ in range(3):  # the second one-token step of a batch size captures its graph
+            m.step([(q, [1]) for q in seqs])
+        ms = timer(lambda: m.step([(q, [1]) for q in seqs]), steps=16)
+        out["decode_b%d_ctx%d_tok_s" % (nb, ctx)] = round(nb / ms * 1e3)
+        out["decode_b%d_ms_per_step" % nb] = round(ms, 4)
+    fresh(0)
+    del m
+    torch.cuda.empty_cache()
+    # ---- the closest prompt-cache model at equal width, depth, heads and feed-forward (fp16, batch of one) ----
+    lc = LlamaConfigLite(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"], num_hidden_layers=len(cfg["layers"]),
+                         num_attention_heads=s["width"] // 128, num_key_value_heads=s["G"], max_position_embeddings=prompt + ctx + 64)
+    ll = LlamaForCausalLM(lc, device=dev)
+    ids = torch.tensor([p1], device=dev)
+    pos = torch.arange(prompt, device=dev).unsqueeze(0)
+    ms = timer(lambda: ll(input_ids=ids, position_ids=pos, use_cache=True, max_position=prompt - 1), steps=5)
+    out["llama_prefill_1x%d_tok_s" % prompt] = round(prompt / ms * 1e3)
+    cids, cpos = torch.tensor([toks(ctx)], device=dev), torch.arange(ctx, device=dev).unsqueeze(0)
+    state = {"past": ll(input_ids=cids, position_ids=cpos, use_cache=True, max_position=ctx - 1).past_key_values, "n": ctx}
+    one = torch.tensor([[1]], device=dev)
+
+    def llama_decode():
+        o = ll(input_ids=one, position_ids=torch.tensor([[state["n"]]], device=dev), past_key_values=state["past"], use_cache=True,
+               max_position=state["n"])
+        state["past"], state["n"] = o.past_key_values, state["n"] + 1
+
+    for _ in range(3):
+        llama_decode()
+    ms = timer(llama_decode, steps=16)
+    out["llama_decode_b1_ctx%d_tok_s" % ctx] = round(1 / ms * 1e3)
+    out["llama_decode_b1_ms_per_step"] = round(ms, 4)
+    del ll
+    torch.cuda.empty_cache()
+    return out
+
+
+def kernel_block(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: float, tflops: float) -> dict:
+    """Every kernel of the new design alone at this size, achieved / peak, beside the like kernel of the Llama path."""
+    from . import _native as nat, _native_seq as nsq
+    bf, H, G, D, V, W = torch.bfloat16, s["H"], s["G"], s["D"], s["V"], s["width"]
+    out = {}
+    cap = ((max(prompt, ctx + 1) + 127) // 128) * 128
+    kp, vp = torch.randn(1, G, cap, D, device=dev).to(bf), torch.randn(1, G, cap, V, device=dev).to(bf)
+    r1, r2 = torch.full((H,), 0.5, device=dev), torch.full((H,), 0.5, device=dev)
+    # attention over a prompt: FLOPs = 2 (D + V) per (query, visible key) pair and head
+    b = nsq.Batch([0], [0], [prompt], dev)
+    q, o = torch.randn(prompt, H * D, device=dev).to(bf), torch.empty(prompt, H * V, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, r1, r2, True, b))
+    fl = 2.0 * (D + V) * H * prompt * (prompt + 1) / 2
+    out["attn_prompt"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_measured_bf16_peak": round(fl / ms / 1e9 / tflops, 3)}
+    ql = torch.randn(H, prompt, 128, device=dev).half()
+    kl, vl = torch.randn(G, cap, 128, device=dev).half(), torch.randn(G, cap, 128, device=dev).half()
+    ol = torch.empty(prompt, H * 128, device=dev, dtype=torch.half)
+    ws = torch.zeros(nat.attn_workspace_bytes(H, prompt, 128), dtype=torch.uint8, device=dev)
+    ms = timer(lambda: nat.attention(ql, kl, vl, ol, 0, prompt, H, G, 128, 128 ** -0.5, 0, workspace=ws))
+    fl = 4.0 * 128 * H * prompt * (prompt + 1) / 2
+    out["llama_attn_prompt"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_measured_bf16_peak": round(fl / ms / 1e9 / tflops, 3)}
+    # attention of one decoded token over ctx keys: bytes = K and V rows of every kv head
+    b1 = nsq.Batch([0], [ctx], [1], dev)
+    q1, o1 = torch.randn(1, H * D, device=dev).to(bf), torch.empty(1, H * V, device=dev, dtype=bf)
+    wsd = nsq.attn_workspace(1, H, V, dev)
+    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, r1, r2, True, b1, max_keys=cap, workspace=wsd), steps=15)
+    by = 2.0 * G * (ctx + 1) * (D + V)
+    out["attn_decode"] = {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    ql1, ol1 = torch.randn(H, 1, 128, device=dev).half(), torch.empty(1, H * 128, device=dev, dtype=torch.half)
+    ws1 = torch.zeros(nat.attn_workspace_bytes(H, 1, 128), dtype=torch.uint8, device=dev)
+    ms = timer(lambda: nat.attention(ql1, kl, vl, ol1, ctx, 1, H, G, 128, 128 ** -0.5, 0, workspace=ws1, decode=True), steps=15)
+    by = 2.0 * G * (ctx + 1) * 256
+    out["llama_attn_decode"] = {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    # gated output norm + residual + next norm over a prompt: reads y, g (2 B), x (4 B), writes x (4 B), h (2 B)
+    x, y, gl = torch.randn(prompt, W, device=dev), torch.randn(prompt, W, device=dev).to(bf), torch.randn(prompt, W, device=dev).to(bf)
+    wn, h = torch.ones(W, device=dev, dtype=bf), torch.empty(prompt, W, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.gate_norm_add(x, y, gl, wn, wn, 1e-5, wn, h))
+    by = prompt * W * 14.0
+    out["gate_norm_add"] = {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    xh, dh, hh, wh = (torch.randn(prompt, W, device=dev).half(), torch.randn(prompt, W, device=dev).half(),
+                      torch.empty(prompt, W, device=dev, dtype=torch.half), torch.ones(W, device=dev, dtype=torch.half))
+    ms = timer(lambda: nat.add_rmsnorm(xh, dh, wh, hh, 1e-5))
+    by = prompt * W * 8.0
+    out["llama_add_rmsnorm"] = {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    # matrix-memory scan over a prompt (sequential in the tokens) and of one decoded token (state read + written once)
+    mH, mD, mV = s["mH"], s["mD"], s["mV"]
+    proj = (torch.randn(prompt, 2 * mH * mD + 2 * mH * mV, device=dev) * 0.3).to(bf)
+    offs = (0, mH * mD, 2 * mH * mD, 2 * mH * mD + mH * mV)
+    ig, fg = torch.randn(prompt, mH, device=dev), -torch.rand(prompt, mH, device=dev) * 0.1
+    sp, npool, mp = torch.zeros(1, mH, mD, mV, device=dev), torch.zeros(1, mH, mD, device=dev), torch.zeros(1, mH, device=dev)
+    nw, om = torch.ones(mH * mV, device=dev, dtype=bf), torch.empty(prompt, mH * mV, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.mlstm_scan(proj, offs, ig, fg, nw, om, sp, npool, mp, 1e-5, b), steps=5)
+    out["mlstm_scan_prompt"] = {"ms": round(ms, 3), "us_per_token": round(ms * 1e3 / prompt, 3),
+                                "gflops": round(4.0 * mH * mD * mV * prompt / ms / 1e6, 1)}
+    ms = timer(lambda: nsq.mlstm_scan(proj[:1], offs, ig[:1], fg[:1], nw, om[:1], sp, npool, mp, 1e-5, b1), steps=15)
+    by = 8.0 * mH * mD * mV
+    out["mlstm_scan_decode"] = {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    return out
+
+
+def run(args, load_peaks, ClockSampler) -> None:
+    from . import _native as nat, _native_seq as nsq, build as pc_build
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pc_build.build()
+    nat.load()
+    nsq.load()
+    hbm, kind, tfl = load_peaks()
+    timer = Timer(dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark()
+    before = nat.launch_count() + nsq.launch_count()
+    line = {"design": "mutolix", "compared_with": "llama (fp16 prompt-cache path) at equal width, depth, kv heads and feed-forward",
+            "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "kind": kind},
+            "timing": "CUDA events, 3 warm-up iterations, 256 MiB L2 flush between iterations, median", "sizes": {}}
+    prompt, batch, ctx = 2048, 4, 2048
+    for name, s in SIZES.items():
+        blk = model_block(name, s, dev, timer, prompt, batch, ctx)
+        blk["kernels"] = kernel_block(s, dev, timer, prompt, ctx, hbm, tfl)
+        line["sizes"][name] = blk
+    line["gpu_launches"] = nat.launch_count() + nsq.launch_count() - before
+    line["clocks"] = sampler.stop()
+    print(json.dumps(line), flush=True)

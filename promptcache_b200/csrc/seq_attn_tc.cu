@@ -1,7 +1,8 @@
 // Tensor-core attention over the slot pool for prompts (bfloat16 storage).
 //
 // One block = 64 consecutive new tokens of one sequence and one head, 4 warps of 16 query rows each; keys in tiles of 64.
-// Q, K and V tiles are staged in shared memory (rows padded by 16 bytes), fragments come from ldmatrix, products are
+// Q, K and V tiles are staged in shared memory (rows padded by 16 bytes; K and V in two cp.async stages, the next tile
+// travels while the current one is multiplied), fragments come from ldmatrix, products are
 // m16n8k16 bfloat16 tensor-core operations with 32-bit accumulators held in registers:
 //     S = Q K^T           32-bit scores; scale, distance bias r1 ln(1 + r2 (i - j)) and the causal mask applied per score
 //     online softmax      running maximum / sum per query row in 32-bit; a sink starts them at (0, 1) instead of (-inf, 0)
@@ -32,13 +33,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
-// P = hi + lo in bfloat16: returns the packed hi pair, `lo_pair` gets the packed remainders
+// P = hi + lo in bfloat16: returns the packed hi pair, `lo_pair` gets the packed remainders (the hi halves are widened back
+// with integer operations: one conversion instruction per pair and part)
 __device__ __forceinline__ uint32_t split_pair(float p0, float p1, uint32_t& lo_pair) {
-  const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
-  lo_pair = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
-  const __nv_bfloat162 v = __halves2bfloat162(h0, h1);
-  return *reinterpret_cast<const uint32_t*>(&v);
+  const uint32_t hi = pack_bf16(p0, p1);
+  lo_pair = pack_bf16(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
+  return hi;
 }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // rows [row0, row0 + 64) x `width` of a [*, src_stride] bfloat16 matrix into a [64][WP + PAD] tile; rows >= n_rows and
 // columns >= width are zero
@@ -54,13 +62,27 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat1
   }
 }
 
+// the same through cp.async (the caller commits and waits)
+template <int WP>
+__device__ __forceinline__ void load_tile_async(__nv_bfloat16* dst, const __nv_bfloat16* src, long long src_stride, int row0, int n_rows,
+                                                int width) {
+  constexpr int CH = WP / 8;
+  for (int e = threadIdx.x; e < BM * CH; e += TC_THREADS) {
+    const int r = e / CH, c = (e - r * CH) * 8;
+    __nv_bfloat16* d = dst + r * (WP + PAD) + c;
+    if (row0 + r < n_rows && c < width) cp_async16(d, src + static_cast<long long>(row0 + r) * src_stride + c);
+    else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 template <int DP, int VP>
 __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* Ks = Qs + BM * (DP + PAD);
-  __nv_bfloat16* Vs = Ks + BN * (DP + PAD);
-  const int b = blockIdx.y, h = blockIdx.z, q0 = blockIdx.x * BM;
+  __nv_bfloat16* Kbuf = Qs + BM * (DP + PAD);       // two stages of K, then two of V
+  __nv_bfloat16* Vbuf = Kbuf + 2 * BN * (DP + PAD);
+  // the longest blocks (last rows of a prompt: most key tiles) are scheduled first
+  const int b = blockIdx.y, h = blockIdx.z, q0 = (gridDim.x - 1 - blockIdx.x) * BM;
   const int len = p.seq_len[b];
   if (q0 >= len) return;
   const int pos0 = p.seq_pos0[b], off = p.seq_off[b], slot = p.seq_slot[b];
@@ -84,14 +106,22 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
   for (int i = 0; i < VP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const uint32_t q_base = static_cast<uint32_t>(__cvta_generic_to_shared(Qs)) +
                           ((warp * 16 + (lane & 15)) * (DP + PAD) + (lane >> 4) * 8) * 2;
-  const uint32_t k_base = static_cast<uint32_t>(__cvta_generic_to_shared(Ks)) + (((lane & 7)) * (DP + PAD) + (lane >> 3) * 8) * 2;
-  const uint32_t v_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs)) + ((lane & 15) * (VP + PAD) + (lane >> 4) * 8) * 2;
+  const uint32_t k_base0 = static_cast<uint32_t>(__cvta_generic_to_shared(Kbuf)) + (((lane & 7)) * (DP + PAD) + (lane >> 3) * 8) * 2;
+  const uint32_t v_base0 = static_cast<uint32_t>(__cvta_generic_to_shared(Vbuf)) + ((lane & 15) * (VP + PAD) + (lane >> 4) * 8) * 2;
+  load_tile_async<DP>(Kbuf, Kg, D, 0, total_keys, D);
+  load_tile_async<VP>(Vbuf, Vg, V, 0, total_keys, V);
+  cp_async_commit();
 
-  for (int k0 = 0; k0 < n_keys; k0 += BN) {
-    __syncthreads();  // the previous tile's fragments have been read (and Q is complete on the first pass)
-    load_tile<DP>(Ks, Kg, D, k0, total_keys, D);
-    load_tile<VP>(Vs, Vg, V, k0, total_keys, V);
-    __syncthreads();
+  for (int k0 = 0, it = 0; k0 < n_keys; k0 += BN, ++it) {
+    const int st = it & 1;
+    if (k0 + BN < n_keys) {  // the next tile travels while this one is multiplied
+      load_tile_async<DP>(Kbuf + (st ^ 1) * BN * (DP + PAD), Kg, D, k0 + BN, total_keys, D);
+      load_tile_async<VP>(Vbuf + (st ^ 1) * BN * (VP + PAD), Vg, V, k0 + BN, total_keys, V);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();  // this tile (and Q on the first pass) is complete for every warp
+    const uint32_t k_base = k_base0 + st * BN * (DP + PAD) * 2, v_base = v_base0 + st * BN * (VP + PAD) * 2;
     // ---- S = Q K^T: 16 rows x 64 keys per warp ----
     float s[BN / 8][4];
 #pragma unroll
@@ -111,6 +141,9 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
     }
     // ---- scale, distance bias, causal mask; row maxima ----
     float mx_a = -INFINITY, mx_b = -INFINITY;
+    // distance of this thread's first key of the tile from each of its two rows, as floats (exact below 2^24); the
+    // per-score distance subtracts a compile-time constant
+    const float dq_a = static_cast<float>(pq_a - k0 - qd * 2), dq_b = static_cast<float>(pq_b - k0 - qd * 2);
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
@@ -121,7 +154,8 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
         if (pk > pq || pk >= total_keys) {
           v = -INFINITY;
         } else if (bias) {
-          v -= r1 * __logf(fmaf(r2, static_cast<float>(pq - pk), 1.f));
+          const float dist = ((e < 2) ? dq_a : dq_b) - static_cast<float>(nt * 8 + (e & 1));
+          v -= r1 * __logf(fmaf(r2, dist, 1.f));
         }
         s[nt][e] = v;
         if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
@@ -170,6 +204,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
         mma_bf16(o[vn + 1], lo0, lo1, lo2, lo3, b2, b3);
       }
     }
+    __syncthreads();  // every warp has read this stage: the tile after the next may overwrite it
   }
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
@@ -191,7 +226,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
 
 template <int DP, int VP>
 int launch(const pcs_attn_params& p, cudaStream_t st) {
-  const size_t smem = (static_cast<size_t>(BM + BN) * (DP + PAD) + static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16);
+  const size_t smem = (static_cast<size_t>(BM + 2 * BN) * (DP + PAD) + 2 * static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
     PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

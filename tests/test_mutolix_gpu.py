@@ -215,7 +215,7 @@ def test_qk_prep_norm_temperature_mixing_append(nsq, every):
     assert float(kp[0].abs().max()) == 0 and float(kp[slot, :, :pos0].abs().max()) == 0 and float(kp[slot, :, pos0 + T:].abs().max()) == 0
 
 
-@pytest.mark.parametrize("H,D,V", [(2, 8, 16), (1, 16, 8), (3, 12, 20), (2, 64, 128), (1, 16, 160)])
+@pytest.mark.parametrize("H,D,V", [(2, 8, 16), (1, 16, 8), (3, 12, 20), (2, 64, 128), (1, 16, 160), (1, 200, 24), (1, 260, 16)])
 def test_mlstm_gates_and_scan(nsq, H, D, V):
     """The recurrence in one piece, in portions through the pooled state, and as single tokens; large gate values reach
     the cap and the running maximum."""
@@ -237,12 +237,13 @@ def test_mlstm_gates_and_scan(nsq, H, D, V):
     k, v = proj[:, offs[1]:offs[2]].reshape(T, H, D), proj[:, offs[2]:offs[3]].reshape(T, H, V)
     o, state = O.mlstm_recurrence(q, k, v, ig_o, fg_o)
     want = O.rms(o, eps).reshape(T, H * V) * nw * torch.sigmoid(proj[:, offs[3]:offs[3] + H * V])
-    for cuts in ([T], [5, 2, 1, 29], [1] * T):
+    for cuts, impl in (([T], 0), ([5, 2, 1, 29], 0), ([1] * T, 0), ([T], 1), ([7, 30], 1)):   # impl 1: the state in shared memory
         s, n, m = torch.full((3, H, D, V), 7.0, device=DEV), torch.full((3, H, D), 7.0, device=DEV), torch.full((3, H), 7.0, device=DEV)
         out, lo = torch.empty(T, H * V, device=DEV), 0
         for c in cuts:          # slot 2 is dirty: a sequence that holds no tokens must start from zero all the same
             batch = nsq.Batch([2], [lo], [c], torch.device(DEV))
-            nsq.mlstm_scan(dev(proj[lo:lo + c]), offs, ig[lo:lo + c].contiguous(), fg[lo:lo + c].contiguous(), dev(nw), out[lo:lo + c], s, n, m, eps, batch)
+            nsq.mlstm_scan(dev(proj[lo:lo + c]), offs, ig[lo:lo + c].contiguous(), fg[lo:lo + c].contiguous(), dev(nw), out[lo:lo + c], s, n, m, eps, batch,
+                           impl=impl)
             lo += c
         close(out, want, 2e-5, f"scan cut {cuts[:4]}")
         close(s[2], state[0], 2e-5, "S")
