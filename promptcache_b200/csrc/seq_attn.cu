@@ -160,6 +160,134 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   }
 }
 
+// Few tokens over many keys (decoding).  One block per (token, head, split of the keys), tiles of 128 keys:
+//   scores    one key per thread, its row read in 16-byte pieces with several loads in flight;
+//   maximum   one barrier (warp maxima through shared memory), weights w = exp(s - m) into shared memory, one more barrier;
+//   values    a thread owns one 16-byte piece of the value row and every R-th key of the tile (R = 128 / pieces per row),
+//             so a warp reads whole rows; the denominator is summed the same way.  The R partial sums meet once, at the end.
+// Needs dim and vdim to be multiples of a 16-byte piece and at most 128 pieces per value row; other shapes take the plain kernel.
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_attn_params p) {
+  constexpr int N = Vec<T>::n;
+  extern __shared__ float sm[];  // q[dim], w[128], partial sums [128 * N]
+  __shared__ float red[kAttnThreads / 32];
+  __shared__ float lred[kAttnThreads];
+  float* qs = sm;
+  float* ws = sm + p.dim;
+  float* part_s = ws + kAttnThreads;
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
+  const int g = h / (p.n_heads / p.n_kv_heads);
+  const int D = p.dim, V = p.vdim;
+  const T* q = static_cast<const T*>(p.q) + (static_cast<long long>(t) * p.n_heads + h) * D;
+  const T* K = static_cast<const T*>(p.k_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * D;
+  const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
+  for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
+  const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
+  const int n_keys = pos + 1, S = gridDim.z, sp = blockIdx.z;
+  const int chunk = ((n_keys + S - 1) / S + kAttnThreads - 1) / kAttnThreads * kAttnThreads;
+  const int k_begin = sp * chunk, k_end = min(n_keys, k_begin + chunk);
+  const bool sink_here = p.sink && sp == 0;
+  const int CH = V / N, R = kAttnThreads / CH;  // pieces per value row, keys handled side by side
+  const int c = tid % CH, r = tid / CH;
+  const bool active = r < R;
+  float m = sink_here ? 0.f : -INFINITY;
+  float lsum = (sink_here && tid == 0) ? 1.f : 0.f;
+  float acc[N];
+#pragma unroll
+  for (int e = 0; e < N; ++e) acc[e] = 0.f;
+  __syncthreads();
+  for (int j0 = k_begin; j0 < k_end; j0 += kAttnThreads) {
+    const int j = j0 + tid;
+    float s = -INFINITY;
+    if (j < k_end) {
+      const T* kr = K + static_cast<long long>(j) * D;
+      float a0 = 0.f, a1 = 0.f;
+      int d = 0;
+      for (; d + 4 * N <= D; d += 4 * N) {
+        float k0[N], k1[N], k2[N], k3[N];
+        ld16(kr + d, k0); ld16(kr + d + N, k1); ld16(kr + d + 2 * N, k2); ld16(kr + d + 3 * N, k3);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+          a0 = fmaf(qs[d + e], k0[e], a0);
+          a1 = fmaf(qs[d + N + e], k1[e], a1);
+        }
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+          a0 = fmaf(qs[d + 2 * N + e], k2[e], a0);
+          a1 = fmaf(qs[d + 3 * N + e], k3[e], a1);
+        }
+      }
+      for (; d < D; d += N) {
+        float k0[N];
+        ld16(kr + d, k0);
+#pragma unroll
+        for (int e = 0; e < N; ++e) a0 = fmaf(qs[d + e], k0[e], a0);
+      }
+      s = (a0 + a1) * p.scale;
+      if (p.bias_r1) s -= r1 * log1pf(r2 * static_cast<float>(pos - j));
+    }
+    const float wm = warp_max(s);
+    if ((tid & 31) == 0) red[tid >> 5] = wm;
+    __syncthreads();
+    float tmax = red[0];
+#pragma unroll
+    for (int i = 1; i < kAttnThreads / 32; ++i) tmax = fmaxf(tmax, red[i]);
+    const float m_new = fmaxf(m, tmax);  // finite: a tile has at least one key
+    const float f = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    m = m_new;
+    ws[tid] = (j < k_end) ? expf(s - m_new) : 0.f;
+    __syncthreads();
+    if (active) {
+      const int nt = min(kAttnThreads, k_end - j0);
+      lsum *= f;
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc[e] *= f;
+      const T* vr = Vp + static_cast<long long>(j0) * V + c * N;
+      int jj = r;
+      for (; jj + 3 * R < nt; jj += 4 * R) {
+        float v0[N], v1[N], v2[N], v3[N];
+        ld16(vr + static_cast<long long>(jj) * V, v0);
+        ld16(vr + static_cast<long long>(jj + R) * V, v1);
+        ld16(vr + static_cast<long long>(jj + 2 * R) * V, v2);
+        ld16(vr + static_cast<long long>(jj + 3 * R) * V, v3);
+        const float w0 = ws[jj], w1 = ws[jj + R], w2 = ws[jj + 2 * R], w3 = ws[jj + 3 * R];
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] = fmaf(w3, v3[e], fmaf(w2, v2[e], fmaf(w1, v1[e], fmaf(w0, v0[e], acc[e]))));
+        lsum += (w0 + w1) + (w2 + w3);
+      }
+      for (; jj < nt; jj += R) {
+        float v0[N];
+        ld16(vr + static_cast<long long>(jj) * V, v0);
+        const float w0 = ws[jj];
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] = fmaf(w0, v0[e], acc[e]);
+        lsum += w0;
+      }
+    }
+    // the next tile writes `red` after this tile's second barrier and `ws` after its own first one: no barrier here
+  }
+  // the R partial sums of every column, and of the denominator (one per key group: the threads of piece 0)
+  if (active) {
+#pragma unroll
+    for (int e = 0; e < N; ++e) part_s[r * V + c * N + e] = acc[e];
+  }
+  lred[tid] = (active && c == 0) ? lsum : 0.f;
+  __syncthreads();
+  float l = 0.f;
+  for (int i = 0; i < kAttnThreads; ++i) l += lred[i];
+  float* part = (S > 1) ? p.workspace + ((static_cast<long long>(t) * p.n_heads + h) * S + sp) * (V + 2) : nullptr;
+  if (part && tid == 0) { part[0] = m; part[1] = l; }
+  T* o = static_cast<T*>(p.out) + (static_cast<long long>(t) * p.n_heads + h) * V;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int col = tid; col < V; col += kAttnThreads) {
+    float a = 0.f;
+    for (int rr = 0; rr < R; ++rr) a += part_s[rr * V + col];
+    if (part) part[2 + col] = a;
+    else stf(o + col, a * inv);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads) attn_combine_kernel(const pcs_attn_params p, int S) {
   const int t = blockIdx.x, h = blockIdx.y, V = p.vdim;
@@ -228,12 +356,15 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
   }
   const size_t smem = static_cast<size_t>(p->dim + pcs::kAttnThreads) * sizeof(float);
   PCS_REQUIRE(smem <= 48 * 1024, "pcs_attn: dim %d exceeds the shared-memory query row", p->dim);
-  // few tokens over many keys (decoding): the keys are split so that the launch fills the GPU; each split has >= 256 keys
+  // few tokens over many keys (decoding): the keys are split so that the launch fills the GPU; each split has >= 128 keys
+  const int piece = p->dtype == PCS_BF16 ? 8 : 4;
+  const bool decode = p->impl == 0 && p->workspace != nullptr && p->dim % piece == 0 && p->vdim % piece == 0 &&
+                      p->vdim / piece <= pcs::kAttnThreads;
   int splits = 1;
   if (p->workspace != nullptr && p->max_keys > 512) {
     const long long blocks = static_cast<long long>(p->n_tokens) * p->n_heads;
     const int want = static_cast<int>((2 * 148 + blocks - 1) / blocks);
-    splits = p->max_keys / 256;
+    splits = p->max_keys / (decode ? 128 : 256);
     if (splits > want) splits = want;
     if (splits > pcs::kAttnMaxSplits) splits = pcs::kAttnMaxSplits;
     if (splits < 1) splits = 1;
@@ -241,7 +372,12 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
                 "pcs_attn: workspace too small for %d splits", splits);
   }
   dim3 grid(p->n_tokens, p->n_heads, splits);
-  PCS_DISPATCH(p->dtype, pcs::attn_plain_kernel<T><<<grid, pcs::kAttnThreads, smem, st>>>(*p));
+  if (decode) {
+    const size_t smem_d = smem + static_cast<size_t>(pcs::kAttnThreads) * piece * sizeof(float);
+    PCS_DISPATCH(p->dtype, pcs::attn_decode_kernel<T><<<grid, pcs::kAttnThreads, smem_d, st>>>(*p));
+  } else {
+    PCS_DISPATCH(p->dtype, pcs::attn_plain_kernel<T><<<grid, pcs::kAttnThreads, smem, st>>>(*p));
+  }
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   if (splits > 1) {

@@ -11,35 +11,13 @@
 // Key / value widths are padded in shared memory to 64, 128 or 256 (zero fill); every width that is a multiple of 8 up to
 // 256 is served.  Other types and shapes fall to the plain kernel (seq_attn.cu).
 #include "seq_common.cuh"
+#include "seq_mma.cuh"
 
 namespace pcs {
 
 namespace {
 
 constexpr int BM = 64, BN = 64, TC_THREADS = 128, PAD = 8;
-
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-// P = hi + lo in bfloat16: returns the packed hi pair, `lo_pair` gets the packed remainders (the hi halves are widened back
-// with integer operations: one conversion instruction per pair and part)
-__device__ __forceinline__ uint32_t split_pair(float p0, float p1, uint32_t& lo_pair) {
-  const uint32_t hi = pack_bf16(p0, p1);
-  lo_pair = pack_bf16(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
-  return hi;
-}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))), "l"(gmem) : "memory");
@@ -99,6 +77,13 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
   // this thread's two query rows (grp, grp + 8 of the warp's 16) and their positions
   const int row_a = warp * 16 + grp, row_b = row_a + 8;
   const int pq_a = pos0 + q0 + row_a, pq_b = pos0 + q0 + row_b;
+  // the bias r1 ln(1 + r2 d) depends on the distance d = i - j alone: 127 distances per tile, computed once per tile into
+  // shared memory in the base-2 domain (r1 log2(1 + r2 d)).  A thread's two scores of an 8-key group are neighbours in
+  // the table; two copies, one shifted by an entry, keep every thread's float2 read aligned whatever its row's parity.
+  float* T0 = reinterpret_cast<float*>(Vbuf + 2 * BN * (VP + PAD));
+  float* T1 = T0 + 128;
+  const float* tp_a = (row_a & 1) ? T0 + (63 - row_a + qd * 2) : T1 + (62 - row_a + qd * 2);
+  const float scale2 = p.scale * 1.4426950408889634f;
   float m_a = p.sink ? 0.f : -INFINITY, m_b = m_a;
   float l_a = (p.sink && qd == 0) ? 1.f : 0.f, l_b = l_a;  // per-thread share of the row sums; the sink's 1 sits in one lane
   float o[VP / 8][4];
@@ -119,10 +104,16 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
       load_tile_async<VP>(Vbuf + (st ^ 1) * BN * (VP + PAD), Vg, V, k0 + BN, total_keys, V);
     }
     cp_async_commit();
+    if (bias) {  // this tile's distance biases, one per thread: entry y belongs to distance (q0 - k0) + 63 - y
+      const int y = threadIdx.x, d = pos0 + q0 - k0 + 63 - y;
+      const float v = d >= 0 ? r1 * __log2f(fmaf(r2, static_cast<float>(d), 1.f)) : 0.f;
+      T0[y] = v;
+      if (y > 0) T1[y - 1] = v;
+    }
     cp_async_wait<1>();
-    __syncthreads();  // this tile (and Q on the first pass) is complete for every warp
+    __syncthreads();  // this tile (and Q on the first pass), and its bias table, are complete for every warp
     const uint32_t k_base = k_base0 + st * BN * (DP + PAD) * 2, v_base = v_base0 + st * BN * (VP + PAD) * 2;
-    // ---- S = Q K^T: 16 rows x 64 keys per warp ----
+    // ---- S = Q K^T: 16 rows x 64 keys per warp; four independent accumulators between two products into the same one ----
     float s[BN / 8][4];
 #pragma unroll
     for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -132,53 +123,59 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
       ldsm_x4(q_base + kk * 32, a0, a1, a2, a3);
       ldsm_x4(q_base + (kk + 1) * 32, c0, c1, c2, c3);
 #pragma unroll
-      for (int nt = 0; nt < BN / 8; ++nt) {
-        uint32_t b0, b1, b2, b3;  // keys nt*8.., dims kk*16.. (b0,b1) and (kk+1)*16.. (b2,b3)
-        ldsm_x4(k_base + (nt * 8 * (DP + PAD) + kk * 16) * 2, b0, b1, b2, b3);
-        mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
-        mma_bf16(s[nt], c0, c1, c2, c3, b2, b3);
+      for (int nt = 0; nt < BN / 8; nt += 4) {
+        uint32_t kf[4][4];  // keys (nt + u)*8.., dims kk*16.. ([0],[1]) and (kk+1)*16.. ([2],[3])
+#pragma unroll
+        for (int u = 0; u < 4; ++u) ldsm_x4(k_base + ((nt + u) * 8 * (DP + PAD) + kk * 16) * 2, kf[u][0], kf[u][1], kf[u][2], kf[u][3]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mma_bf16(s[nt + u], a0, a1, a2, a3, kf[u][0], kf[u][1]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mma_bf16(s[nt + u], c0, c1, c2, c3, kf[u][2], kf[u][3]);
       }
     }
-    // ---- scale, distance bias, causal mask; row maxima ----
+    // ---- scores in the base-2 domain: s * scale * log2(e) - bias (from the tile's table); causal mask only where a tile
+    //      reaches past the warp's first row or the last key; row maxima ----
+    const bool need_mask = (k0 + BN - 1 > pos0 + q0 + warp * 16) || (k0 + BN > total_keys);
     float mx_a = -INFINITY, mx_b = -INFINITY;
-    // distance of this thread's first key of the tile from each of its two rows, as floats (exact below 2^24); the
-    // per-score distance subtracts a compile-time constant
-    const float dq_a = static_cast<float>(pq_a - k0 - qd * 2), dq_b = static_cast<float>(pq_b - k0 - qd * 2);
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int pk = k0 + nt * 8 + qd * 2 + (e & 1);
-        const int pq = (e < 2) ? pq_a : pq_b;
-        float v = s[nt][e] * p.scale;
-        if (pk > pq || pk >= total_keys) {
-          v = -INFINITY;
-        } else if (bias) {
-          const float dist = ((e < 2) ? dq_a : dq_b) - static_cast<float>(nt * 8 + (e & 1));
-          v -= r1 * __logf(fmaf(r2, dist, 1.f));
-        }
-        s[nt][e] = v;
-        if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+      float2 ba = make_float2(0.f, 0.f), bb = ba;
+      if (bias) {
+        ba = *reinterpret_cast<const float2*>(tp_a + nt * 8);
+        bb = *reinterpret_cast<const float2*>(tp_a + nt * 8 - 8);
       }
+      s[nt][0] = fmaf(s[nt][0], scale2, -ba.x);
+      s[nt][1] = fmaf(s[nt][1], scale2, -ba.y);
+      s[nt][2] = fmaf(s[nt][2], scale2, -bb.x);
+      s[nt][3] = fmaf(s[nt][3], scale2, -bb.y);
+      if (need_mask) {
+        const int pk = k0 + nt * 8 + qd * 2;
+        if (pk > pq_a || pk >= total_keys) s[nt][0] = -INFINITY;
+        if (pk + 1 > pq_a || pk + 1 >= total_keys) s[nt][1] = -INFINITY;
+        if (pk > pq_b || pk >= total_keys) s[nt][2] = -INFINITY;
+        if (pk + 1 > pq_b || pk + 1 >= total_keys) s[nt][3] = -INFINITY;
+      }
+      mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
+      mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
     }
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    // key 0 is visible to every row, so the maxima are finite from the first tile on; a masked score gives 2^-inf = 0
     const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-    const float f_a = (m_a == -INFINITY) ? 0.f : __expf(m_a - mn_a), f_b = (m_b == -INFINITY) ? 0.f : __expf(m_b - mn_b);
+    const float f_a = (m_a == -INFINITY) ? 0.f : ex2(m_a - mn_a), f_b = (m_b == -INFINITY) ? 0.f : ex2(m_b - mn_b);
     m_a = mn_a;
     m_b = mn_b;
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float mn = (e < 2) ? mn_a : mn_b;
-        const float w = (s[nt][e] == -INFINITY) ? 0.f : __expf(s[nt][e] - mn);
-        s[nt][e] = w;
-        if (e < 2) sum_a += w; else sum_b += w;
-      }
+      s[nt][0] = ex2(s[nt][0] - mn_a);
+      s[nt][1] = ex2(s[nt][1] - mn_a);
+      s[nt][2] = ex2(s[nt][2] - mn_b);
+      s[nt][3] = ex2(s[nt][3] - mn_b);
+      sum_a += s[nt][0] + s[nt][1];
+      sum_b += s[nt][2] + s[nt][3];
     }
     l_a = l_a * f_a + sum_a;
     l_b = l_b * f_b + sum_b;
@@ -186,7 +183,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
     for (int i = 0; i < VP / 8; ++i) {
       o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b;
     }
-    // ---- O += P V, P as hi + lo ----
+    // ---- O += P V, P as hi + lo; four value-column tiles between the hi and the lo product of one accumulator ----
 #pragma unroll
     for (int j = 0; j < BN / 16; ++j) {
       uint32_t lo0, lo1, lo2, lo3;
@@ -195,13 +192,20 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
       const uint32_t hi2 = split_pair(s[2 * j + 1][0], s[2 * j + 1][1], lo2);
       const uint32_t hi3 = split_pair(s[2 * j + 1][2], s[2 * j + 1][3], lo3);
 #pragma unroll
-      for (int vn = 0; vn < VP / 8; vn += 2) {
-        uint32_t b0, b1, b2, b3;  // keys j*16.., value columns vn*8.. (b0,b1) and (vn+1)*8.. (b2,b3)
-        ldsm_x4_t(v_base + (j * 16 * (VP + PAD) + vn * 8) * 2, b0, b1, b2, b3);
-        mma_bf16(o[vn], hi0, hi1, hi2, hi3, b0, b1);
-        mma_bf16(o[vn], lo0, lo1, lo2, lo3, b0, b1);
-        mma_bf16(o[vn + 1], hi0, hi1, hi2, hi3, b2, b3);
-        mma_bf16(o[vn + 1], lo0, lo1, lo2, lo3, b2, b3);
+      for (int vn = 0; vn < VP / 8; vn += 4) {
+        uint32_t vf[2][4];  // keys j*16.., value columns (vn + 2u)*8.. ([0],[1]) and (vn + 2u + 1)*8.. ([2],[3])
+#pragma unroll
+        for (int u = 0; u < 2; ++u) ldsm_x4_t(v_base + (j * 16 * (VP + PAD) + (vn + 2 * u) * 8) * 2, vf[u][0], vf[u][1], vf[u][2], vf[u][3]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          mma_bf16(o[vn + 2 * u], hi0, hi1, hi2, hi3, vf[u][0], vf[u][1]);
+          mma_bf16(o[vn + 2 * u + 1], hi0, hi1, hi2, hi3, vf[u][2], vf[u][3]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          mma_bf16(o[vn + 2 * u], lo0, lo1, lo2, lo3, vf[u][0], vf[u][1]);
+          mma_bf16(o[vn + 2 * u + 1], lo0, lo1, lo2, lo3, vf[u][2], vf[u][3]);
+        }
       }
     }
     __syncthreads();  // every warp has read this stage: the tile after the next may overwrite it
@@ -226,7 +230,8 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
 
 template <int DP, int VP>
 int launch(const pcs_attn_params& p, cudaStream_t st) {
-  const size_t smem = (static_cast<size_t>(BM + 2 * BN) * (DP + PAD) + 2 * static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16);
+  const size_t smem = (static_cast<size_t>(BM + 2 * BN) * (DP + PAD) + 2 * static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16) +
+                      256 * sizeof(float);
   static bool configured = false;
   if (!configured) {
     PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

@@ -26,11 +26,26 @@ __global__ void __launch_bounds__(256) mlstm_gates_kernel(const T* __restrict__ 
                                                           float* __restrict__ fg, int width, int heads, float cap) {
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const T* hr = h + t * h_stride;
+  constexpr int N = Vec<T>::n;
+  const bool vec = width % N == 0 && (h_stride * sizeof(T)) % 16 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w_i) |
+                                                                             reinterpret_cast<uintptr_t>(w_f)) & 15) == 0;
   for (int o = warp; o < 2 * heads; o += nw) {
     const int head = o >> 1, is_f = o & 1;
     const T* w = (is_f ? w_f : w_i) + static_cast<long long>(head) * width;
     float a = 0.f;
-    for (int i = lane; i < width; i += 32) a = fmaf(ldf(hr + i), ldf(w + i), a);
+    if (vec) {  // 16-byte pieces, two accumulators
+      float a1 = 0.f;
+      for (int i = lane * N; i < width; i += 32 * N) {
+        float hv[N], wv[N];
+        ld16(hr + i, hv);
+        ld16(w + i, wv);
+#pragma unroll
+        for (int e = 0; e < N; e += 2) { a = fmaf(hv[e], wv[e], a); a1 = fmaf(hv[e + 1], wv[e + 1], a1); }
+      }
+      a += a1;
+    } else {
+      for (int i = lane; i < width; i += 32) a = fmaf(ldf(hr + i), ldf(w + i), a);
+    }
     a = warp_sum(a);
     if (lane == 0) {
       const float z = cap * tanhf((a + (is_f ? b_f[head] : b_i[head])) / cap);

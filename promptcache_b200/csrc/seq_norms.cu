@@ -83,6 +83,115 @@ __global__ void __launch_bounds__(256) gate_norm_add_kernel(const pcs_gna_params
   for (int i = threadIdx.x; i < W; i += blockDim.x) stf(h + i, u[i] * inv2 * ldf(nw + i));
 }
 
+__device__ __forceinline__ void ldx(const float* p, float (&o)[4]) { ld16(p, o); }
+__device__ __forceinline__ void ldx(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void stx(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void stx(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void st16(float* p, const float (&v)[4]) { stx(p, v); }
+__device__ __forceinline__ void st16(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// The same row operation for rows of at most 256 * PPT 16-byte pieces whose pointers and strides are 16-byte aligned: a
+// thread keeps its pieces in registers, and EVERY operand (y, the gate, x, the three weight vectors) is requested before the
+// first reduction, so that one memory round trip is exposed instead of three.
+template <typename T, int PPT>
+__global__ void __launch_bounds__(256) gate_norm_add_vec_kernel(const pcs_gna_params p) {
+  constexpr int N = Vec<T>::n;
+  __shared__ float red[33];
+  const int r = blockIdx.x, W = p.width;
+  const T* y = static_cast<const T*>(p.y) + static_cast<long long>(r) * p.y_stride;
+  const T* g = p.g ? static_cast<const T*>(p.g) + static_cast<long long>(r) * p.g_stride : nullptr;
+  const T* w = static_cast<const T*>(p.w);
+  const T* ls = static_cast<const T*>(p.ls);
+  const T* nw = static_cast<const T*>(p.next_w);
+  float* x = p.x + static_cast<long long>(r) * W;
+  float v[PPT][N], wv[PPT][N], lv[PPT][N], xv[PPT][N], nv[PPT][N];
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    const int i = (threadIdx.x + u * 256) * N;
+    if (i < W) {
+      ld16(y + i, v[u]);
+      ld16(w + i, wv[u]);
+      ldx(x + i, xv[u]);
+      if (ls) ld16(ls + i, lv[u]);
+      if (nw) ld16(nw + i, nv[u]);
+      if (g) {
+        float gv[N];
+        ld16(g + i, gv);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v[u][e] *= sigmoidf_(gv[e]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u)
+    if ((threadIdx.x + u * 256) * N < W) {
+#pragma unroll
+      for (int e = 0; e < N; ++e) ss = fmaf(v[u][e], v[u][e], ss);
+    }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(W) + p.eps);
+  float s2 = 0.f;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    const int i = (threadIdx.x + u * 256) * N;
+    if (i < W) {
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        float t = v[u][e] * inv * wv[u][e];
+        if (ls) t *= lv[u][e];
+        xv[u][e] += t;
+        s2 = fmaf(xv[u][e], xv[u][e], s2);
+      }
+      stx(x + i, xv[u]);
+    }
+  }
+  if (nw == nullptr) return;
+  s2 = block_sum(s2, red);
+  const float inv2 = 1.f / sqrtf(s2 / static_cast<float>(W) + p.eps);
+  T* h = static_cast<T*>(p.h_out) + static_cast<long long>(r) * W;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    const int i = (threadIdx.x + u * 256) * N;
+    if (i < W) {
+      float o[N];
+#pragma unroll
+      for (int e = 0; e < N; ++e) o[e] = xv[u][e] * inv2 * nv[u][e];
+      st16(h + i, o);
+    }
+  }
+}
+
+// 16-byte pieces: `width`, both strides and both pointers are multiples of a piece
+template <typename T>
+__global__ void __launch_bounds__(256) xielu_vec_kernel(const T* __restrict__ z, long long z_stride, T* __restrict__ out,
+                                                        long long out_stride, const T* __restrict__ a, int width) {
+  constexpr int N = Vec<T>::n;
+  const int r = blockIdx.x;
+  const float ap = softplusf_(ldf(a)), an = 0.5f + softplusf_(ldf(a + 1));
+  const T* zr = z + r * z_stride;
+  T* o = out + r * out_stride;
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * N; i < width; i += gridDim.y * blockDim.x * N) {
+    float v[N], f[N];
+    ld16(zr + i, v);
+#pragma unroll
+    for (int e = 0; e < N; ++e) f[e] = v[e] > 0.f ? fmaf(ap * v[e], v[e], 0.5f * v[e]) : fmaf(an, expm1f(v[e]) - v[e], 0.5f * v[e]);
+    st16(o + i, f);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) xielu_kernel(const T* __restrict__ z, long long z_stride, T* __restrict__ out,
                                                     long long out_stride, const T* __restrict__ a, int width) {
@@ -137,6 +246,20 @@ PCS_API int pcs_gate_norm_add(const pcs_gna_params* p, void* stream) {
     PCS_DISPATCH(p->dtype, PCS_CHECK_CUDA(cudaFuncSetAttribute(pcs::gate_norm_add_kernel<T>,
                                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
   }
+  // rows that fit the register kernel (at most 512 aligned 16-byte pieces) take it
+  const int piece = p->dtype == PCS_BF16 ? 8 : 4;
+  const long long esz = p->dtype == PCS_BF16 ? 2 : 4;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = p->width % piece == 0 && p->width <= 512 * piece && (p->y_stride * esz) % 16 == 0 && al(p->x) && al(p->y) && al(p->w) &&
+                   (p->g == nullptr || (al(p->g) && (p->g_stride * esz) % 16 == 0)) && (p->ls == nullptr || al(p->ls)) &&
+                   (p->next_w == nullptr || (al(p->next_w) && al(p->h_out)));
+  if (vec) {
+    if (p->width <= 256 * piece) PCS_DISPATCH(p->dtype, pcs::gate_norm_add_vec_kernel<T, 1><<<p->n_rows, 256, 0, st>>>(*p));
+    else PCS_DISPATCH(p->dtype, pcs::gate_norm_add_vec_kernel<T, 2><<<p->n_rows, 256, 0, st>>>(*p));
+    PCS_CHECK_CUDA(cudaGetLastError());
+    pcs::count_launch();
+    return PCS_OK;
+  }
   PCS_DISPATCH(p->dtype, pcs::gate_norm_add_kernel<T><<<p->n_rows, 256, smem, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
@@ -148,6 +271,18 @@ PCS_API int pcs_xielu(const void* z, int64_t z_stride, void* out, int64_t out_st
   if (n_rows == 0) return PCS_OK;
   PCS_REQUIRE(z && out && a && n_rows > 0 && width > 0, "pcs_xielu: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int piece = dtype == PCS_BF16 ? 8 : 4;
+  const long long esz = dtype == PCS_BF16 ? 2 : 4;
+  if (width % piece == 0 && (z_stride * esz) % 16 == 0 && (out_stride * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const int per_row = (width / piece + 255) / 256;
+    dim3 vgrid(n_rows, per_row > 64 ? 64 : per_row);
+    PCS_DISPATCH(dtype, pcs::xielu_vec_kernel<T><<<vgrid, 256, 0, st>>>(static_cast<const T*>(z), z_stride, static_cast<T*>(out), out_stride,
+                                                                        static_cast<const T*>(a), width));
+    PCS_CHECK_CUDA(cudaGetLastError());
+    pcs::count_launch();
+    return PCS_OK;
+  }
   dim3 grid(n_rows, (width + 255) / 256 > 64 ? 64 : (width + 255) / 256);
   PCS_DISPATCH(dtype, pcs::xielu_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(z), z_stride, static_cast<T*>(out), out_stride,
                                                                  static_cast<const T*>(a), width));
