@@ -148,7 +148,8 @@ typedef struct pcs_mlstm_params {
   const int32_t* seq_off;
   int32_t n_seqs, dtype;
   int32_t max_len;          /* host upper bound of the new tokens of one entry */
-  int32_t impl;             /* 0 = automatic, 1 = the token-by-token kernel */
+  int32_t impl;             /* 0 = automatic, 1 = token by token with the state in shared memory, 2 = token by token (registers
+                               where the sizes allow): never the chunkwise tensor-core kernel */
   float* o_raw;             /* fp32 scratch of n_tokens*heads*vdim + n_seqs*heads*(dim+1) elements: the recurrence's result before
                                the per-head norm, and the new n / m of every entry until they are committed */
   int32_t n_tokens, reserved;

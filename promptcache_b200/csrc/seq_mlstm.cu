@@ -396,6 +396,11 @@ __global__ void __launch_bounds__(256) mlstm_out_kernel(const pcs_mlstm_params p
 
 }  // namespace pcs
 
+namespace pcs {
+int launch_mlstm_chunk(const pcs_mlstm_params& p, float* nm_new, cudaStream_t st);
+constexpr int kChunkMinLen = 24;  // shorter steps (decoding, tails of a prompt) go token by token
+}  // namespace pcs
+
 PCS_API int pcs_mlstm_gates(const void* h, int64_t h_stride, const void* w_i, const void* w_f, const float* b_i, const float* b_f,
                             float* ig, float* fg, int n_tokens, int width, int heads, float cap, int dtype, void* stream) {
   if (n_tokens == 0) return PCS_OK;
@@ -419,7 +424,10 @@ PCS_API int pcs_mlstm_scan(const pcs_mlstm_params* p, void* stream) {
   const int es = p->dtype == PCS_BF16 ? 2 : 4, per = 16 / es;
   const bool aligned = p->dim % per == 0 && p->vdim % per == 0 && p->q_off % per == 0 && p->k_off % per == 0 && p->v_off % per == 0 &&
                        p->row_stride % per == 0 && reinterpret_cast<uintptr_t>(p->proj) % 16 == 0;
-  if (p->impl == 0 && p->dim <= 256 && aligned) {
+  if (p->impl == 0 && p->dtype == PCS_BF16 && aligned && p->dim % 16 == 0 && p->dim <= 256 && p->max_len >= pcs::kChunkMinLen) {
+    // prompts in bfloat16: 64 tokens at a time on the tensor cores
+    if (int rc = pcs::launch_mlstm_chunk(*p, nm_new, st)) return rc;
+  } else if (p->impl != 1 && p->dim <= 256 && aligned) {
     // register-resident state: warps per block halve until the launch has two blocks per SM (or 2 warps are left)
     int W = 16;
     while (W > 1 && 8 * (W / 2) >= p->vdim) W /= 2;

@@ -252,6 +252,69 @@ def test_mlstm_gates_and_scan(nsq, H, D, V):
         assert float(s[0].min()) == 7.0  # other slots untouched
 
 
+@pytest.mark.parametrize("H,D,V,cuts", [
+    (2, 16, 8, [64]), (1, 32, 40, [63, 65]), (2, 64, 64, [130, 1, 1, 70]), (1, 48, 24, [24, 200]), (1, 256, 72, [129]), (3, 128, 32, [64, 64, 5, 100]),
+])
+def test_mlstm_chunkwise_bf16(nsq, H, D, V, cuts):
+    """The chunkwise tensor-core form (bfloat16 projections, steps of 24 tokens and more) against the token-by-token
+    oracle on the SAME bfloat16-rounded projections: chunk edges at 63 / 64 / 65 tokens, steps that continue a pooled state
+    (also one left by single-token steps), gates that reach the cap, a dirty slot, and the state it leaves behind.  The
+    32-bit factors enter the tensor cores as hi + lo pairs, so the result is 32-bit accurate, far inside bfloat16 rounding."""
+    torch.manual_seed(D + V)
+    T, eps = sum(cuts), 1e-5
+    proj = (torch.randn(T, 2 * H * D + 2 * H * V + 8) * 0.5).to(BF16)
+    offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
+    ig_o = (torch.randn(T, H, dtype=O.F64) * 3).clamp(-6, 6)
+    fg_o = -torch.rand(T, H, dtype=O.F64) * 0.3
+    fg_o[T // 3] = -5.0   # one token nearly wipes the state
+    nw = torch.randn(H * V).to(BF16)
+    p64 = proj.to(O.F64)
+    q = (p64[:, :H * D] * D ** -0.5).view(T, H, D)
+    k, v = p64[:, offs[1]:offs[2]].reshape(T, H, D), p64[:, offs[2]:offs[3]].reshape(T, H, V)
+    o, state = O.mlstm_recurrence(q, k, v, ig_o, fg_o)
+    want = O.rms(o, eps).reshape(T, H * V) * nw.to(O.F64) * torch.sigmoid(p64[:, offs[3]:offs[3] + H * V])
+    ig, fg = dev(ig_o), dev(fg_o)
+    for impl in (0, 2):   # 2: never the chunkwise kernel (the same inputs token by token)
+        s, n, m = torch.full((2, H, D, V), 7.0, device=DEV), torch.full((2, H, D), 7.0, device=DEV), torch.full((2, H), 7.0, device=DEV)
+        out, lo = torch.empty(T, H * V, device=DEV, dtype=BF16), 0
+        for c in cuts:
+            batch = nsq.Batch([1], [lo], [c], torch.device(DEV))
+            nsq.mlstm_scan(proj[lo:lo + c].to(DEV), offs, ig[lo:lo + c].contiguous(), fg[lo:lo + c].contiguous(), nw.to(DEV), out[lo:lo + c], s, n, m,
+                           eps, batch, impl=impl)
+            lo += c
+        close(s[1], state[0], 3e-5, f"S (impl {impl})")
+        close(n[1], state[1], 3e-5, f"n (impl {impl})")
+        close(m[1], state[2], 1e-6, f"m (impl {impl})")
+        close(out, want, 6e-3, f"output (impl {impl})")   # the output itself is rounded to bfloat16
+        assert float(s[0].min()) == 7.0
+
+
+def test_mlstm_chunkwise_batch_of_unequal_entries(nsq):
+    """Entries of 100, 3 and 64 tokens in one launch, the second and third continuing pooled states: each equals the entry alone."""
+    torch.manual_seed(3)
+    H, D, V, eps = 2, 32, 48, 1e-5
+    lens, pos0, slots = [100, 3, 64], [0, 40, 9], [2, 0, 1]
+    T = sum(lens)
+    proj = (torch.randn(T, 2 * H * D + 2 * H * V) * 0.5).to(BF16).to(DEV)
+    offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
+    ig, fg = torch.randn(T, H, device=DEV), -torch.rand(T, H, device=DEV) * 0.2
+    nw = torch.randn(H * V).to(BF16).to(DEV)
+    s0, n0, m0 = torch.randn(3, H, D, V, device=DEV), torch.randn(3, H, D, device=DEV), torch.rand(3, H, device=DEV)
+    s, n, m = s0.clone(), n0.clone(), m0.clone()
+    out = torch.empty(T, H * V, device=DEV, dtype=BF16)
+    nsq.mlstm_scan(proj, offs, ig, fg, nw, out, s, n, m, eps, nsq.Batch(slots, pos0, lens, torch.device(DEV)))
+    lo = 0
+    for b, c in enumerate(lens):
+        s1, n1, m1 = s0.clone(), n0.clone(), m0.clone()
+        o1 = torch.empty(c, H * V, device=DEV, dtype=BF16)
+        nsq.mlstm_scan(proj[lo:lo + c], offs, ig[lo:lo + c].contiguous(), fg[lo:lo + c].contiguous(), nw, o1, s1, n1, m1, eps,
+                       nsq.Batch([slots[b]], [pos0[b]], [c], torch.device(DEV)), impl=2)
+        close(out[lo:lo + c], o1.cpu(), 6e-3, f"entry {b}")
+        close(s[slots[b]], s1[slots[b]].cpu(), 3e-5, f"state of entry {b}")
+        close(n[slots[b]], n1[slots[b]].cpu(), 3e-5, f"n of entry {b}")
+        lo += c
+
+
 # ---- whole models (float32 rounding accumulates over the layers: 1e-4 of the largest value) ---------------------------
 def test_whole_prompt_fp32_layers_and_logits(tmp_path):
     cfg, W = O.random_model(LAYERS(), width=40, vocab=61, seed=1)
