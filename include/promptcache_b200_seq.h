@@ -128,6 +128,11 @@ int pcs_attn(const pcs_attn_params* p, void* stream);
 int pcs_mlstm_gates(const void* h, int64_t h_stride, const void* w_i, const void* w_f, const float* b_i, const float* b_f,
                     float* ig, float* fg, int n_tokens, int width, int heads, float cap, int dtype, void* stream);
 
+/* out[m, n] = sum_k x[m, k] w[n, k] + bias[n] for 1 to 8 rows (decoding): the weights are streamed once, sums are fp32.
+   k, the row stride of x and the pointers of x and w must be multiples of 16 bytes. */
+int pcs_linear_rows(const void* x, int64_t x_stride, const void* w, const void* bias, void* out, int64_t out_stride, int m, int n, int k,
+                    int dtype, void* stream);
+
 typedef struct pcs_mlstm_params {
   const void* proj;         /* [n_tokens, row_stride]: q at q_off, k at k_off, v at v_off, output-gate pre-activation at g_off */
   int64_t row_stride;

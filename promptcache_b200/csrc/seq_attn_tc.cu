@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
   // shared memory in the base-2 domain (r1 log2(1 + r2 d)).  A thread's two scores of an 8-key group are neighbours in
   // the table; two copies, one shifted by an entry, keep every thread's float2 read aligned whatever its row's parity.
   float* T0 = reinterpret_cast<float*>(Vbuf + 2 * BN * (VP + PAD));
-  float* T1 = T0 + 128;
+  float* T1 = T0 + 144;  // 16 banks away from T0: the odd and the even rows of a warp read different banks
   const float* tp_a = (row_a & 1) ? T0 + (63 - row_a + qd * 2) : T1 + (62 - row_a + qd * 2);
   const float scale2 = p.scale * 1.4426950408889634f;
   float m_a = p.sink ? 0.f : -INFINITY, m_b = m_a;
@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
     cp_async_wait<1>();
     __syncthreads();  // this tile (and Q on the first pass), and its bias table, are complete for every warp
     const uint32_t k_base = k_base0 + st * BN * (DP + PAD) * 2, v_base = v_base0 + st * BN * (VP + PAD) * 2;
-    // ---- S = Q K^T: 16 rows x 64 keys per warp; four independent accumulators between two products into the same one ----
+    // ---- S = Q K^T: 16 rows x 64 keys per warp; eight independent accumulators between two products into the same one ----
     float s[BN / 8][4];
 #pragma unroll
     for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -122,15 +122,14 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
       uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
       ldsm_x4(q_base + kk * 32, a0, a1, a2, a3);
       ldsm_x4(q_base + (kk + 1) * 32, c0, c1, c2, c3);
+      {
+        uint32_t kf[BN / 8][4];  // keys u*8.., dims kk*16.. ([0],[1]) and (kk+1)*16.. ([2],[3])
 #pragma unroll
-      for (int nt = 0; nt < BN / 8; nt += 4) {
-        uint32_t kf[4][4];  // keys (nt + u)*8.., dims kk*16.. ([0],[1]) and (kk+1)*16.. ([2],[3])
+        for (int u = 0; u < BN / 8; ++u) ldsm_x4(k_base + (u * 8 * (DP + PAD) + kk * 16) * 2, kf[u][0], kf[u][1], kf[u][2], kf[u][3]);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) ldsm_x4(k_base + ((nt + u) * 8 * (DP + PAD) + kk * 16) * 2, kf[u][0], kf[u][1], kf[u][2], kf[u][3]);
+        for (int u = 0; u < BN / 8; ++u) mma_bf16(s[u], a0, a1, a2, a3, kf[u][0], kf[u][1]);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) mma_bf16(s[nt + u], a0, a1, a2, a3, kf[u][0], kf[u][1]);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) mma_bf16(s[nt + u], c0, c1, c2, c3, kf[u][2], kf[u][3]);
+        for (int u = 0; u < BN / 8; ++u) mma_bf16(s[u], c0, c1, c2, c3, kf[u][2], kf[u][3]);
       }
     }
     // ---- scores in the base-2 domain: s * scale * log2(e) - bias (from the tile's table); causal mask only where a tile
@@ -183,7 +182,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
     for (int i = 0; i < VP / 8; ++i) {
       o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b;
     }
-    // ---- O += P V, P as hi + lo; four value-column tiles between the hi and the lo product of one accumulator ----
+    // ---- O += P V, P as hi + lo; eight value-column tiles between the hi and the lo product of one accumulator ----
 #pragma unroll
     for (int j = 0; j < BN / 16; ++j) {
       uint32_t lo0, lo1, lo2, lo3;
@@ -192,17 +191,17 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
       const uint32_t hi2 = split_pair(s[2 * j + 1][0], s[2 * j + 1][1], lo2);
       const uint32_t hi3 = split_pair(s[2 * j + 1][2], s[2 * j + 1][3], lo3);
 #pragma unroll
-      for (int vn = 0; vn < VP / 8; vn += 4) {
-        uint32_t vf[2][4];  // keys j*16.., value columns (vn + 2u)*8.. ([0],[1]) and (vn + 2u + 1)*8.. ([2],[3])
+      for (int vn = 0; vn < VP / 8; vn += 8) {
+        uint32_t vf[4][4];  // keys j*16.., value columns (vn + 2u)*8.. ([0],[1]) and (vn + 2u + 1)*8.. ([2],[3])
 #pragma unroll
-        for (int u = 0; u < 2; ++u) ldsm_x4_t(v_base + (j * 16 * (VP + PAD) + (vn + 2 * u) * 8) * 2, vf[u][0], vf[u][1], vf[u][2], vf[u][3]);
+        for (int u = 0; u < 4; ++u) ldsm_x4_t(v_base + (j * 16 * (VP + PAD) + (vn + 2 * u) * 8) * 2, vf[u][0], vf[u][1], vf[u][2], vf[u][3]);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < 4; ++u) {
           mma_bf16(o[vn + 2 * u], hi0, hi1, hi2, hi3, vf[u][0], vf[u][1]);
           mma_bf16(o[vn + 2 * u + 1], hi0, hi1, hi2, hi3, vf[u][2], vf[u][3]);
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < 4; ++u) {
           mma_bf16(o[vn + 2 * u], lo0, lo1, lo2, lo3, vf[u][0], vf[u][1]);
           mma_bf16(o[vn + 2 * u + 1], lo0, lo1, lo2, lo3, vf[u][2], vf[u][3]);
         }
@@ -231,7 +230,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
 template <int DP, int VP>
 int launch(const pcs_attn_params& p, cudaStream_t st) {
   const size_t smem = (static_cast<size_t>(BM + 2 * BN) * (DP + PAD) + 2 * static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16) +
-                      256 * sizeof(float);
+                      272 * sizeof(float);
   static bool configured = false;
   if (!configured) {
     PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

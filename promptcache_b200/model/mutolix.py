@@ -10,8 +10,9 @@ scaled per channel and added to the 32-bit residual stream).  The mixers:
               term in the softmax denominator, and values optionally mixed with those of the first such layer
               (`pcs_qk_prep`, `pcs_attn`).
 
-The feed-forward is W_down xIELU(W_up h).  Projections are library matrix products (one per sublayer input with the
-gate's rows fused in, one per sublayer output); everything between them runs in the sequence-batch kernels.  Sizes, the
+The feed-forward is W_down xIELU(W_up h).  Projections (one per sublayer input with the gate's rows fused in, one per
+sublayer output) are library matrix products for prompts and `pcs_linear_rows`, which streams the weights once, for the
+one to eight rows of a decoding step; everything between them runs in the sequence-batch kernels.  Sizes, the
 order of layers and every constant come from config.json; tensors are named l<i>.norm1, l<i>.mix.q, ... in the checkpoint.
 """
 from __future__ import annotations
@@ -21,7 +22,6 @@ import os
 from typing import Dict, List, Optional
 
 import torch
-import torch.nn.functional as F
 
 from .. import _native_seq as nsq
 from .. import weights as wio
@@ -167,7 +167,7 @@ class MutolixForCausalLM(SlotPoolCausalLM):
         for i, blk in enumerate(self.blocks):
             st = self.pool.layers[i]
             nxt = self.blocks[i + 1]["norm1"] if i + 1 < len(self.blocks) else None
-            proj = F.linear(h, blk["w_in"], blk["b_in"])
+            proj = nsq.linear(h, blk["w_in"], blk["b_in"])
             H, V = blk["heads"], blk["vdim"]
             mixed = torch.empty(T, H * V, dtype=dt, device=dev)
             if blk["type"] == "mlstm":
@@ -186,16 +186,16 @@ class MutolixForCausalLM(SlotPoolCausalLM):
                 ws = nsq.attn_workspace(T, H, V, dev) if T <= 16 else None
                 nsq.attention(q, st["k"], st["v"], mixed, H, blk["scale"], blk["r1"], blk["r2"], True, batch, impl=self.attn_impl,
                               max_keys=self.pool.cap, workspace=ws)
-            y = F.linear(mixed, blk["w_o"])
+            y = nsq.linear(mixed, blk["w_o"])
             gate = proj[:, blk["rg_off"]:] if blk["gated1"] else None
             has_ff = blk["ff"] > 0
             nsq.gate_norm_add(x, y, gate, blk["norm1b"], blk["ls1"], eps, blk["norm2"] if has_ff else nxt, h if (has_ff or nxt is not None) else None)
             if has_ff:
                 ff = blk["ff"]
-                u = F.linear(h, blk["w_up"], blk["b_up"])
+                u = nsq.linear(h, blk["w_up"], blk["b_up"])
                 a = torch.empty(T, ff, dtype=dt, device=dev)
                 nsq.xielu(u[:, :ff], a, blk["act"])
-                d = F.linear(a, blk["w_down"])
+                d = nsq.linear(a, blk["w_down"])
                 nsq.gate_norm_add(x, d, u[:, ff:] if blk["gated2"] else None, blk["norm2b"], blk["ls2"], eps, nxt, h if nxt is not None else None)
             if self.layer_trace is not None:
                 self.layer_trace.append(x.clone())
@@ -203,4 +203,4 @@ class MutolixForCausalLM(SlotPoolCausalLM):
             return torch.zeros(0, self.vocab_size, dtype=torch.float32, device=dev)
         hw = torch.empty(rows.numel(), W, dtype=dt, device=dev)
         nsq.rmsnorm(x, self.final_norm, hw, eps, rows=rows)
-        return F.linear(hw, self.head).float()
+        return nsq.linear(hw, self.head).float()

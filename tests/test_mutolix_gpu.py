@@ -252,6 +252,22 @@ def test_mlstm_gates_and_scan(nsq, H, D, V):
         assert float(s[0].min()) == 7.0  # other slots untouched
 
 
+@pytest.mark.parametrize("dtype,tol", [(F32, 2e-6), (BF16, 6e-3)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 8), (2, 33, 520), (3, 64, 1024), (5, 10, 264), (8, 129, 96), (9, 12, 64)])
+def test_linear_of_few_rows(nsq, dtype, tol, M, N, K):
+    """One to eight rows through the weight-streaming kernel (feature counts that are not a multiple of a block's eight, K that
+    is not a multiple of a block's pass, a strided input); nine rows take the library product.  Sums are 32-bit in both types."""
+    torch.manual_seed(M * N + K)
+    x = torch.randn(M, K + 16).to(dtype)
+    w, b = (torch.randn(N, K) / K ** 0.5).to(dtype), torch.randn(N).to(dtype)
+    for bias in (b, None):
+        got = nsq.linear(x.to(DEV)[:, 8:8 + K] if dtype == BF16 else x.to(DEV)[:, 4:4 + K], w.to(DEV), bias.to(DEV) if bias is not None else None,
+                         kernel=True)
+        xs = x[:, 8:8 + K] if dtype == BF16 else x[:, 4:4 + K]
+        want = xs.to(O.F64) @ w.to(O.F64).T + (bias.to(O.F64) if bias is not None else 0)
+        close(got, want, tol, f"linear {M}x{N}x{K}")
+
+
 @pytest.mark.parametrize("H,D,V,cuts", [
     (2, 16, 8, [64]), (1, 32, 40, [63, 65]), (2, 64, 64, [130, 1, 1, 70]), (1, 48, 24, [24, 200]), (1, 256, 72, [129]), (3, 128, 32, [64, 64, 5, 100]),
 ])
