@@ -19,13 +19,6 @@ namespace {
 
 constexpr int BM = 64, BN = 64, TC_THREADS = 128, PAD = 8;
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // rows [row0, row0 + 64) x `width` of a [*, src_stride] bfloat16 matrix into a [64][WP + PAD] tile; rows >= n_rows and
 // columns >= width are zero
 template <int WP>

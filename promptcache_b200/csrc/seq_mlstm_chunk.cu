@@ -94,29 +94,39 @@ __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_p
 
   for (int i0 = 0; i0 < len; i0 += CL) {
     const int nvalid = min(CL, len - i0);
-    // ---- the chunk's q, k, v rows and gates into shared memory ----
+    // ---- the chunk's q, k, v rows and gates into shared memory: every 16-byte piece is an asynchronous copy, so the whole
+    //      tile is in flight at once; the next chunk's rows are asked into L2 meanwhile ----
     for (int e = tid; e < CL * pieces; e += CTHREADS) {
       const int r = e / pieces, c = (e - r * pieces) * 8;
-      uint4 qv = make_uint4(0u, 0u, 0u, 0u), kv = qv;
       if (r < nvalid) {
         const __nv_bfloat16* row = proj + static_cast<long long>(off + i0 + r) * p.row_stride;
-        qv = *reinterpret_cast<const uint4*>(row + p.q_off + head * D + c);
-        kv = *reinterpret_cast<const uint4*>(row + p.k_off + head * D + c);
+        cp_async16(Qs + r * QROW + c, row + p.q_off + head * D + c);
+        cp_async16(Ks + r * QROW + c, row + p.k_off + head * D + c);
+      } else {
+        *reinterpret_cast<uint4*>(Qs + r * QROW + c) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(Ks + r * QROW + c) = make_uint4(0u, 0u, 0u, 0u);
       }
-      *reinterpret_cast<uint4*>(Qs + r * QROW + c) = qv;
-      *reinterpret_cast<uint4*>(Ks + r * QROW + c) = kv;
     }
     for (int e = tid; e < CL * CNT; e += CTHREADS) {
       const int r = e / CNT, c = (e - r * CNT) * 8;
-      uint4 vv = make_uint4(0u, 0u, 0u, 0u);
-      if (r < nvalid) {
-        if (c < CVS) {
-          if (v0 + c < V) vv = *reinterpret_cast<const uint4*>(proj + static_cast<long long>(off + i0 + r) * p.row_stride + p.v_off + head * V + v0 + c);
-        } else if (c == CVS) {
-          vv.x = 0x00003f80u;  // bfloat16 1.0 in column CVS
-        }
+      if (r < nvalid && c < CVS && v0 + c < V) {
+        cp_async16(Vs + r * CROW + c, proj + static_cast<long long>(off + i0 + r) * p.row_stride + p.v_off + head * V + v0 + c);
+      } else {
+        uint4 vv = make_uint4(0u, 0u, 0u, 0u);
+        if (r < nvalid && c == CVS) vv.x = 0x00003f80u;  // bfloat16 1.0 in column CVS
+        *reinterpret_cast<uint4*>(Vs + r * CROW + c) = vv;
       }
-      *reinterpret_cast<uint4*>(Vs + r * CROW + c) = vv;
+    }
+    cp_async_commit();
+    if (i0 + CL < len) {  // one 128-byte line per request: q and k rows of the next chunk, and its value slice
+      const int nxt = min(CL, len - i0 - CL), lines = (D * 2 + 127) / 128;
+      for (int e = tid; e < nxt * lines; e += CTHREADS) {
+        const int r = e / lines, c = (e - r * lines) * 64;
+        const __nv_bfloat16* row = proj + static_cast<long long>(off + i0 + CL + r) * p.row_stride;
+        prefetch_l2(row + p.q_off + head * D + c);
+        prefetch_l2(row + p.k_off + head * D + c);
+        if (c == 0) prefetch_l2(row + p.v_off + head * V + v0);
+      }
     }
     if (tid < CL) {
       const bool ok = tid < nvalid;
@@ -124,6 +134,7 @@ __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_p
       f_s[tid] = ok ? p.fg[t] : 0.f;
       i_s[tid] = ok ? p.ig[t] : -INFINITY;
     }
+    cp_async_wait<0>();
     __syncthreads();
     // ---- warp 0: sums of f, running maxima and the per-token factors (two tokens per lane) ----
     if (warp == 0) {
