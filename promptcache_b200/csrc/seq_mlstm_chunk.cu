@@ -8,7 +8,7 @@
 // and the state after the chunk's last token e is S_e = e^{m_in - g_e} S_in + sum_s e^{a_s - g_e} k_s v_s^T.
 // The normaliser n rides along as ONE MORE VALUE COLUMN whose v is 1: the same products give n_t . q_t and the new n.
 //
-// One block = (sequence, head, 32 value columns), 4 warps, the chunks of the entry one after the other.  Products are
+// One block = (sequence, head, 32 or 16 value columns), 4 warps, the chunks of the entry one after the other.  Products are
 // m16n8k16 bfloat16 tensor-core operations with 32-bit accumulators; q, k, v are bfloat16 already (exact operands), every
 // 32-bit factor (the weights e^{a_s - g_t} (q.k), the state, the weighted values) enters as TWO bfloat16 operands hi + lo.
 // The state itself stays 32-bit in shared memory between chunks and in the pool between steps; gates, sums of gates, maxima
@@ -22,11 +22,10 @@ namespace pcs {
 namespace {
 
 constexpr int CL = 64;         // tokens per chunk
-constexpr int CVS = 32;        // value columns per block
-constexpr int CNC = 48;        // columns of the widened tiles: CVS values, the normaliser's column, zero padding (6 groups of 8)
-constexpr int CROW = CNC + 8;  // bfloat16 elements per row of those tiles (112 bytes: ldmatrix without bank conflicts)
 constexpr int CTHREADS = 128;
-constexpr int CNT = CNC / 8;
+// CVS value columns per block (32, or 16 when 32 would leave most SMs without a block).  The widened tiles have
+// CNC = CVS + 16 columns: the values, the normaliser's column, zero padding (an even number of groups of 8), in rows of
+// CROW = CNC + 8 bfloat16 elements (112 or 80 bytes: ldmatrix without bank conflicts).
 
 __device__ __forceinline__ void split1(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
   hi = __float2bfloat16_rn(x);
@@ -35,8 +34,10 @@ __device__ __forceinline__ void split1(float x, __nv_bfloat16& hi, __nv_bfloat16
 
 }  // namespace
 
+template <int CVS>
 __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_params p, float* __restrict__ o_raw,
                                                                float* __restrict__ nm_new) {
+  constexpr int CNC = CVS + 16, CROW = CNC + 8, CNT = CNC / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = p.dim, V = p.vdim, H = p.heads;
   const int QROW = D + 8;  // bfloat16 elements per row of the q and k tiles
@@ -317,21 +318,30 @@ __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_p
   }
 }
 
-size_t mlstm_chunk_smem(int dim) {
-  return static_cast<size_t>(dim) * CNC * sizeof(float) + (2 * static_cast<size_t>(dim) * CROW + 2 * static_cast<size_t>(CL) * (dim + 8) +
-                                                             3 * static_cast<size_t>(CL) * CROW) * sizeof(__nv_bfloat16) +
+size_t mlstm_chunk_smem(int dim, int cvs) {
+  const size_t cnc = cvs + 16, crow = cnc + 8;
+  return static_cast<size_t>(dim) * cnc * sizeof(float) + (2 * static_cast<size_t>(dim) * crow + 2 * static_cast<size_t>(CL) * (dim + 8) +
+                                                             3 * static_cast<size_t>(CL) * crow) * sizeof(__nv_bfloat16) +
          (7 * CL + 4) * sizeof(float);
 }
 
 int launch_mlstm_chunk(const pcs_mlstm_params& p, float* nm_new, cudaStream_t st) {
-  const size_t smem = mlstm_chunk_smem(p.dim);
   static bool configured = false;
   if (!configured) {
-    PCS_CHECK_CUDA(cudaFuncSetAttribute(mlstm_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    PCS_CHECK_CUDA(cudaFuncSetAttribute(mlstm_chunk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    PCS_CHECK_CUDA(cudaFuncSetAttribute(mlstm_chunk_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     configured = true;
   }
-  dim3 grid(p.n_seqs, p.heads, (p.vdim + CVS - 1) / CVS);
-  mlstm_chunk_kernel<<<grid, CTHREADS, smem, st>>>(p, p.o_raw, nm_new);
+  // 32 columns per block unless that leaves the GPU mostly empty (one long prompt): narrower slices recompute the q . k
+  // scores in more blocks but halve everything else a block does per chunk
+  const long long blocks32 = static_cast<long long>(p.n_seqs) * p.heads * ((p.vdim + 31) / 32);
+  if (blocks32 >= 148 || p.vdim <= 16) {
+    dim3 grid(p.n_seqs, p.heads, (p.vdim + 31) / 32);
+    mlstm_chunk_kernel<32><<<grid, CTHREADS, mlstm_chunk_smem(p.dim, 32), st>>>(p, p.o_raw, nm_new);
+  } else {
+    dim3 grid(p.n_seqs, p.heads, (p.vdim + 15) / 16);
+    mlstm_chunk_kernel<16><<<grid, CTHREADS, mlstm_chunk_smem(p.dim, 16), st>>>(p, p.o_raw, nm_new);
+  }
   PCS_CHECK_CUDA(cudaGetLastError());
   return PCS_OK;
 }

@@ -305,17 +305,22 @@ def test_mlstm_chunkwise_bf16(nsq, H, D, V, cuts):
         assert float(s[0].min()) == 7.0
 
 
-def test_mlstm_chunkwise_batch_of_unequal_entries(nsq):
-    """Entries of 100, 3 and 64 tokens in one launch, the second and third continuing pooled states: each equals the entry alone."""
+@pytest.mark.parametrize("H,D,V,lens,pos0,slots", [
+    (2, 32, 48, [100, 3, 64], [0, 40, 9], [2, 0, 1]),
+    # enough blocks for the 32-column slices (few blocks take 16-column slices)
+    (8, 16, 72, [30, 65, 24, 5, 40, 33, 64, 70, 26, 31], [0, 3, 0, 9, 1, 0, 0, 7, 2, 0], [9, 0, 8, 1, 7, 2, 6, 3, 5, 4]),
+])
+def test_mlstm_chunkwise_batch_of_unequal_entries(nsq, H, D, V, lens, pos0, slots):
+    """Entries of unequal lengths in one launch, some continuing pooled states: each equals the entry alone, token by token."""
     torch.manual_seed(3)
-    H, D, V, eps = 2, 32, 48, 1e-5
-    lens, pos0, slots = [100, 3, 64], [0, 40, 9], [2, 0, 1]
+    eps = 1e-5
     T = sum(lens)
     proj = (torch.randn(T, 2 * H * D + 2 * H * V) * 0.5).to(BF16).to(DEV)
     offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
     ig, fg = torch.randn(T, H, device=DEV), -torch.rand(T, H, device=DEV) * 0.2
     nw = torch.randn(H * V).to(BF16).to(DEV)
-    s0, n0, m0 = torch.randn(3, H, D, V, device=DEV), torch.randn(3, H, D, device=DEV), torch.rand(3, H, device=DEV)
+    ns = len(lens)
+    s0, n0, m0 = torch.randn(ns, H, D, V, device=DEV), torch.randn(ns, H, D, device=DEV), torch.rand(ns, H, device=DEV)
     s, n, m = s0.clone(), n0.clone(), m0.clone()
     out = torch.empty(T, H * V, device=DEV, dtype=BF16)
     nsq.mlstm_scan(proj, offs, ig, fg, nw, out, s, n, m, eps, nsq.Batch(slots, pos0, lens, torch.device(DEV)))
