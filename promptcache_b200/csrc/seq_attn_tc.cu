@@ -1,8 +1,8 @@
 // Tensor-core attention over the slot pool for prompts (bfloat16 storage).
 //
 // One block = 64 consecutive new tokens of one sequence and one head, 4 warps of 16 query rows each; keys in tiles of 64.
-// Q, K and V tiles are staged in shared memory (rows padded by 16 bytes; K and V in two cp.async stages, the next tile
-// travels while the current one is multiplied), fragments come from ldmatrix, products are
+// Q, K and V tiles are staged in shared memory (rows padded by 16 bytes; K in two cp.async stages, the next tile travels
+// while the current one is multiplied; V in one, loaded during the score phase), fragments come from ldmatrix, products are
 // m16n8k16 bfloat16 tensor-core operations with 32-bit accumulators held in registers:
 //     S = Q K^T           32-bit scores; scale, distance bias r1 ln(1 + r2 (i - j)) and the causal mask applied per score
 //     online softmax      running maximum / sum per query row in 32-bit; a sink starts them at (0, 1) instead of (-inf, 0)
@@ -47,10 +47,10 @@ __device__ __forceinline__ void load_tile_async(__nv_bfloat16* dst, const __nv_b
 }
 
 template <int DP, int VP>
-__global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_params p) {
+__global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) attn_tc_kernel(const pcs_attn_params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* Kbuf = Qs + BM * (DP + PAD);       // two stages of K, then two of V
+  __nv_bfloat16* Kbuf = Qs + BM * (DP + PAD);       // two stages of K, then one of V
   __nv_bfloat16* Vbuf = Kbuf + 2 * BN * (DP + PAD);
   // the longest blocks (last rows of a prompt: most key tiles) are scheduled first
   const int b = blockIdx.y, h = blockIdx.z, q0 = (gridDim.x - 1 - blockIdx.x) * BM;
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
   // the bias r1 ln(1 + r2 d) depends on the distance d = i - j alone: 127 distances per tile, computed once per tile into
   // shared memory in the base-2 domain (r1 log2(1 + r2 d)).  A thread's two scores of an 8-key group are neighbours in
   // the table; two copies, one shifted by an entry, keep every thread's float2 read aligned whatever its row's parity.
-  float* T0 = reinterpret_cast<float*>(Vbuf + 2 * BN * (VP + PAD));
+  float* T0 = reinterpret_cast<float*>(Vbuf + BN * (VP + PAD));
   float* T1 = T0 + 144;  // 16 banks away from T0: the odd and the even rows of a warp read different banks
   const float* tp_a = (row_a & 1) ? T0 + (63 - row_a + qd * 2) : T1 + (62 - row_a + qd * 2);
   const float scale2 = p.scale * 1.4426950408889634f;
@@ -87,25 +87,25 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
   const uint32_t k_base0 = static_cast<uint32_t>(__cvta_generic_to_shared(Kbuf)) + (((lane & 7)) * (DP + PAD) + (lane >> 3) * 8) * 2;
   const uint32_t v_base0 = static_cast<uint32_t>(__cvta_generic_to_shared(Vbuf)) + ((lane & 15) * (VP + PAD) + (lane >> 4) * 8) * 2;
   load_tile_async<DP>(Kbuf, Kg, D, 0, total_keys, D);
-  load_tile_async<VP>(Vbuf, Vg, V, 0, total_keys, V);
   cp_async_commit();
 
+  // K in two stages, V in one (three blocks of 4 warps fit an SM at widths up to 128): per tile the copies are committed in
+  // the order V_t, K_{t+1}; K_t is complete when at most those two groups are pending, V_t when at most one is
   for (int k0 = 0, it = 0; k0 < n_keys; k0 += BN, ++it) {
     const int st = it & 1;
-    if (k0 + BN < n_keys) {  // the next tile travels while this one is multiplied
-      load_tile_async<DP>(Kbuf + (st ^ 1) * BN * (DP + PAD), Kg, D, k0 + BN, total_keys, D);
-      load_tile_async<VP>(Vbuf + (st ^ 1) * BN * (VP + PAD), Vg, V, k0 + BN, total_keys, V);
-    }
+    load_tile_async<VP>(Vbuf, Vg, V, k0, total_keys, V);  // has the score phase to arrive
     cp_async_commit();
+    if (k0 + BN < n_keys) load_tile_async<DP>(Kbuf + (st ^ 1) * BN * (DP + PAD), Kg, D, k0 + BN, total_keys, D);
+    cp_async_commit();  // (an empty group after the last tile keeps the counts the same)
     if (bias) {  // this tile's distance biases, one per thread: entry y belongs to distance (q0 - k0) + 63 - y
       const int y = threadIdx.x, d = pos0 + q0 - k0 + 63 - y;
       const float v = d >= 0 ? r1 * __log2f(fmaf(r2, static_cast<float>(d), 1.f)) : 0.f;
       T0[y] = v;
       if (y > 0) T1[y - 1] = v;
     }
-    cp_async_wait<1>();
-    __syncthreads();  // this tile (and Q on the first pass), and its bias table, are complete for every warp
-    const uint32_t k_base = k_base0 + st * BN * (DP + PAD) * 2, v_base = v_base0 + st * BN * (VP + PAD) * 2;
+    cp_async_wait<2>();
+    __syncthreads();  // this K tile (and Q on the first pass), and its bias table, are complete for every warp
+    const uint32_t k_base = k_base0 + st * BN * (DP + PAD) * 2, v_base = v_base0;
     // ---- S = Q K^T: 16 rows x 64 keys per warp; eight independent accumulators between two products into the same one ----
     float s[BN / 8][4];
 #pragma unroll
@@ -175,6 +175,8 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
     for (int i = 0; i < VP / 8; ++i) {
       o[i][0] *= f_a; o[i][1] *= f_a; o[i][2] *= f_b; o[i][3] *= f_b;
     }
+    cp_async_wait<1>();
+    __syncthreads();  // the V tile is complete for every warp
     // ---- O += P V, P as hi + lo; eight value-column tiles between the hi and the lo product of one accumulator ----
 #pragma unroll
     for (int j = 0; j < BN / 16; ++j) {
@@ -200,7 +202,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
         }
       }
     }
-    __syncthreads();  // every warp has read this stage: the tile after the next may overwrite it
+    __syncthreads();  // every warp has read V and this K stage: the next tiles may overwrite them
   }
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(TC_THREADS) attn_tc_kernel(const pcs_attn_para
 
 template <int DP, int VP>
 int launch(const pcs_attn_params& p, cudaStream_t st) {
-  const size_t smem = (static_cast<size_t>(BM + 2 * BN) * (DP + PAD) + 2 * static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16) +
+  const size_t smem = (static_cast<size_t>(BM + 2 * BN) * (DP + PAD) + static_cast<size_t>(BN) * (VP + PAD)) * sizeof(__nv_bfloat16) +
                       272 * sizeof(float);
   static bool configured = false;
   if (!configured) {
