@@ -74,6 +74,103 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const pcs_qkprep_params p)
   }
 }
 
+// The same with 16-byte pieces (head sizes, offsets, the row stride and every pointer are multiples of a piece): the sums of
+// squares of q and k share one reduction, a piece of a key or value row never straddles two heads.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prep_vec_kernel(const pcs_qkprep_params p) {
+  constexpr int N = Vec<T>::n;
+  __shared__ float red[2][9];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
+  const T* row = static_cast<const T*>(p.qkv) + static_cast<long long>(t) * p.row_stride;
+  const int nq = p.n_heads * p.dim, nk = p.n_kv_heads * p.dim, nv = p.n_kv_heads * p.vdim;
+  const T* q = row + p.q_off;
+  const T* k = row + p.k_off;
+  float sq = 0.f, sk = 0.f;
+  if (p.q_norm_w)
+    for (int i = tid * N; i < nq; i += 256 * N) {
+      float v[N];
+      ld16(q + i, v);
+#pragma unroll
+      for (int e = 0; e < N; ++e) sq = fmaf(v[e], v[e], sq);
+    }
+  if (p.k_norm_w)
+    for (int i = tid * N; i < nk; i += 256 * N) {
+      float v[N];
+      ld16(k + i, v);
+#pragma unroll
+      for (int e = 0; e < N; ++e) sk = fmaf(v[e], v[e], sk);
+    }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+  __syncthreads();
+  if (warp == 0) {
+    float a = lane < 8 ? red[0][lane] : 0.f, c = lane < 8 ? red[1][lane] : 0.f;
+    a = warp_sum(a);
+    c = warp_sum(c);
+    if (lane == 0) { red[0][8] = a; red[1][8] = c; }
+  }
+  __syncthreads();
+  const float inv_q = p.q_norm_w ? 1.f / sqrtf(red[0][8] / static_cast<float>(nq) + p.eps) : 1.f;
+  const float inv_k = p.k_norm_w ? 1.f / sqrtf(red[1][8] / static_cast<float>(nk) + p.eps) : 1.f;
+  float temp = 1.f;
+  if (p.temp_every > 0) temp = 1.f + p.temp_coef * logf(static_cast<float>((pos + 1) / p.temp_every) + 1.f);
+  {
+    const T* w = static_cast<const T*>(p.q_norm_w);
+    T* qo = static_cast<T*>(p.q_out) + static_cast<long long>(t) * nq;
+    for (int i = tid * N; i < nq; i += 256 * N) {
+      float v[N], wv[N];
+      ld16(q + i, v);
+      if (w) ld16(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        float x = v[e] * inv_q;
+        if (w) x *= wv[e];
+        v[e] = x * temp;
+      }
+      st16(qo + i, v);
+    }
+  }
+  {
+    const T* w = static_cast<const T*>(p.k_norm_w);
+    T* kp = static_cast<T*>(p.k_pool) + static_cast<long long>(slot) * p.n_kv_heads * p.cap * p.dim;
+    for (int i = tid * N; i < nk; i += 256 * N) {
+      float v[N], wv[N];
+      ld16(k + i, v);
+      if (w) ld16(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        float x = v[e] * inv_k;
+        if (w) x *= wv[e];
+        v[e] = x;
+      }
+      const int g = i / p.dim, d = i - g * p.dim;
+      st16(kp + (static_cast<long long>(g) * p.cap + pos) * p.dim + d, v);
+    }
+  }
+  {
+    const T* v = row + p.v_off;
+    const long long base = static_cast<long long>(slot) * p.n_kv_heads * p.cap * p.vdim;
+    T* vp = static_cast<T*>(p.v_pool) + base;
+    const T* vf = p.v_first_pool ? static_cast<const T*>(p.v_first_pool) + base : nullptr;
+    const float lam = vf ? ldf(static_cast<const T*>(p.v_lambda)) : 0.f;
+    for (int i = tid * N; i < nv; i += 256 * N) {
+      const int g = i / p.vdim, d = i - g * p.vdim;
+      const long long o = (static_cast<long long>(g) * p.cap + pos) * p.vdim + d;
+      float x[N];
+      ld16(v + i, x);
+      if (vf) {
+        float f[N];
+        ld16(vf + o, f);
+#pragma unroll
+        for (int e = 0; e < N; ++e) x[e] = (1.f - lam) * x[e] + lam * f[e];
+      }
+      st16(vp + o, x);
+    }
+  }
+}
+
 constexpr int kAttnThreads = 128;
 constexpr int kAttnMaxVPT = 4;  // value columns per thread: vdim <= 512
 
@@ -328,7 +425,13 @@ PCS_API int pcs_qk_prep(const pcs_qkprep_params* p, void* stream) {
               "pcs_qk_prep: bad sizes H=%d Hkv=%d dim=%d vdim=%d cap=%d", p->n_heads, p->n_kv_heads, p->dim, p->vdim, p->cap);
   PCS_REQUIRE(p->v_first_pool == nullptr || p->v_lambda != nullptr, "pcs_qk_prep: value mixing needs lambda");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  PCS_DISPATCH(p->dtype, pcs::qk_prep_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
+  const int piece = p->dtype == PCS_BF16 ? 8 : 4;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = p->dim % piece == 0 && p->vdim % piece == 0 && p->q_off % piece == 0 && p->k_off % piece == 0 && p->v_off % piece == 0 &&
+                   p->row_stride % piece == 0 && al(p->qkv) && al(p->q_out) && al(p->k_pool) && al(p->v_pool) && al(p->q_norm_w) &&
+                   al(p->k_norm_w) && al(p->v_first_pool);
+  if (vec) PCS_DISPATCH(p->dtype, pcs::qk_prep_vec_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
+  else PCS_DISPATCH(p->dtype, pcs::qk_prep_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
