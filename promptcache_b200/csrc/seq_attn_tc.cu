@@ -18,6 +18,7 @@ namespace pcs {
 namespace {
 
 constexpr int BM = 64, BN = 64, TC_THREADS = 128, PAD = 8;
+constexpr int kSMs = 148;  // B200: blocks are handed to the SMs in index order, one per SM and round
 
 // rows [row0, row0 + 64) x `width` of a [*, src_stride] bfloat16 matrix into a [64][WP + PAD] tile; rows >= n_rows and
 // columns >= width are zero
@@ -52,8 +53,18 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Kbuf = Qs + BM * (DP + PAD);       // two stages of K, then one of V
   __nv_bfloat16* Vbuf = Kbuf + 2 * BN * (DP + PAD);
-  // the longest blocks (last rows of a prompt: most key tiles) are scheduled first
-  const int b = blockIdx.y, h = blockIdx.z, q0 = (gridDim.x - 1 - blockIdx.x) * BM;
+  // one-dimensional grid in the order (query tile, sequence, head), the LAST query tiles first: blocks are handed out in
+  // index order, so every head's longest blocks (most key tiles) start in the first wave and the tail is made of short ones
+  const int per_tile = p.n_seqs * p.n_heads, n_qtiles = (p.max_len + BM - 1) / BM;
+  // every second group of 148 blocks (one per SM) runs backwards, so that an SM's first block, one of the longest, shares
+  // the SM with one of the shortest of the next group rather than with another long one
+  int idx = blockIdx.x;
+  {
+    const int wave = idx / kSMs, first = wave * kSMs, last = min(first + kSMs, static_cast<int>(gridDim.x)) - 1;
+    if (wave & 1) idx = first + (last - idx);
+  }
+  const int qt = idx / per_tile, rem = idx - qt * per_tile;
+  const int b = rem / p.n_heads, h = rem - b * p.n_heads, q0 = (n_qtiles - 1 - qt) * BM;
   const int len = p.seq_len[b];
   if (q0 >= len) return;
   const int pos0 = p.seq_pos0[b], off = p.seq_off[b], slot = p.seq_slot[b];
@@ -231,7 +242,7 @@ int launch(const pcs_attn_params& p, cudaStream_t st) {
     PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     configured = true;
   }
-  dim3 grid((p.max_len + BM - 1) / BM, p.n_seqs, p.n_heads);
+  dim3 grid(static_cast<unsigned>((p.max_len + BM - 1) / BM) * p.n_seqs * p.n_heads);
   attn_tc_kernel<DP, VP><<<grid, TC_THREADS, smem, st>>>(p);
   PCS_CHECK_CUDA(cudaGetLastError());
   count_launch();
@@ -250,7 +261,8 @@ int launch_v(const pcs_attn_params& p, cudaStream_t st) {
 int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled) {
   *handled = false;
   if (p.dtype != PCS_BF16 || p.max_len < 16 || p.dim % 8 != 0 || p.vdim % 8 != 0 || p.dim > 256 || p.vdim > 256) return PCS_OK;
-  if (p.n_seqs > 65535 || p.n_heads > 65535 || !p.seq_pos0 || !p.seq_len || !p.seq_off) return PCS_OK;
+  if (!p.seq_pos0 || !p.seq_len || !p.seq_off) return PCS_OK;
+  if (static_cast<long long>((p.max_len + BM - 1) / BM) * p.n_seqs * p.n_heads > 0x7fffffffLL) return PCS_OK;
   *handled = true;
   if (p.dim <= 64) return launch_v<64>(p, st);
   if (p.dim <= 128) return launch_v<128>(p, st);
