@@ -213,15 +213,22 @@ __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_p
     for (int kk = 0; kk < D / 16; ++kk) {
       uint32_t a0, a1, a2, a3;
       ldsm_x4(q_base + kk * 32, a0, a1, a2, a3);
+      // all hi products, then all lo products: CNT independent accumulators between two products into the same one
+      uint32_t hf[CNT / 2][4], lf[CNT / 2][4];
 #pragma unroll
-      for (int vn = 0; vn < CNT; vn += 2) {
-        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-        ldsm_x4_t(sh_base + (kk * 16 * CROW + vn * 8) * 2, h0, h1, h2, h3);
-        ldsm_x4_t(sl_base + (kk * 16 * CROW + vn * 8) * 2, l0, l1, l2, l3);
-        mma_bf16(acc[vn], a0, a1, a2, a3, h0, h1);
-        mma_bf16(acc[vn + 1], a0, a1, a2, a3, h2, h3);
-        mma_bf16(acc[vn], a0, a1, a2, a3, l0, l1);
-        mma_bf16(acc[vn + 1], a0, a1, a2, a3, l2, l3);
+      for (int u = 0; u < CNT / 2; ++u) {
+        ldsm_x4_t(sh_base + (kk * 16 * CROW + u * 16) * 2, hf[u][0], hf[u][1], hf[u][2], hf[u][3]);
+        ldsm_x4_t(sl_base + (kk * 16 * CROW + u * 16) * 2, lf[u][0], lf[u][1], lf[u][2], lf[u][3]);
+      }
+#pragma unroll
+      for (int u = 0; u < CNT / 2; ++u) {
+        mma_bf16(acc[2 * u], a0, a1, a2, a3, hf[u][0], hf[u][1]);
+        mma_bf16(acc[2 * u + 1], a0, a1, a2, a3, hf[u][2], hf[u][3]);
+      }
+#pragma unroll
+      for (int u = 0; u < CNT / 2; ++u) {
+        mma_bf16(acc[2 * u], a0, a1, a2, a3, lf[u][0], lf[u][1]);
+        mma_bf16(acc[2 * u + 1], a0, a1, a2, a3, lf[u][2], lf[u][3]);
       }
     }
     {
@@ -237,14 +244,18 @@ __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_p
       const uint32_t hi1 = split_pair(s[2 * j][2], s[2 * j][3], lo1);
       const uint32_t hi2 = split_pair(s[2 * j + 1][0], s[2 * j + 1][1], lo2);
       const uint32_t hi3 = split_pair(s[2 * j + 1][2], s[2 * j + 1][3], lo3);
+      uint32_t vf[CNT / 2][4];
 #pragma unroll
-      for (int vn = 0; vn < CNT; vn += 2) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4_t(vs_base + (j * 16 * CROW + vn * 8) * 2, b0, b1, b2, b3);
-        mma_bf16(acc[vn], hi0, hi1, hi2, hi3, b0, b1);
-        mma_bf16(acc[vn + 1], hi0, hi1, hi2, hi3, b2, b3);
-        mma_bf16(acc[vn], lo0, lo1, lo2, lo3, b0, b1);
-        mma_bf16(acc[vn + 1], lo0, lo1, lo2, lo3, b2, b3);
+      for (int u = 0; u < CNT / 2; ++u) ldsm_x4_t(vs_base + (j * 16 * CROW + u * 16) * 2, vf[u][0], vf[u][1], vf[u][2], vf[u][3]);
+#pragma unroll
+      for (int u = 0; u < CNT / 2; ++u) {
+        mma_bf16(acc[2 * u], hi0, hi1, hi2, hi3, vf[u][0], vf[u][1]);
+        mma_bf16(acc[2 * u + 1], hi0, hi1, hi2, hi3, vf[u][2], vf[u][3]);
+      }
+#pragma unroll
+      for (int u = 0; u < CNT / 2; ++u) {
+        mma_bf16(acc[2 * u], lo0, lo1, lo2, lo3, vf[u][0], vf[u][1]);
+        mma_bf16(acc[2 * u + 1], lo0, lo1, lo2, lo3, vf[u][2], vf[u][3]);
       }
     }
     // ---- o_t = numerator / (max(|n_t . q_t|, e^{-m_t}) + 1e-6); the denominator's product sits in column CVS ----
@@ -278,15 +289,21 @@ __global__ void __launch_bounds__(CTHREADS) mlstm_chunk_kernel(const pcs_mlstm_p
       for (int ks = 0; ks < CL / 16; ++ks) {
         uint32_t a0, a1, a2, a3;
         ldsm_x4_t(kt_base + (ks * 16 * QROW + mt * 16) * 2, a0, a1, a2, a3);
+        uint32_t hf[CNT / 2][4], lf[CNT / 2][4];
 #pragma unroll
-        for (int vn = 0; vn < CNT; vn += 2) {
-          uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-          ldsm_x4_t(vh_base + (ks * 16 * CROW + vn * 8) * 2, h0, h1, h2, h3);
-          ldsm_x4_t(vl_base + (ks * 16 * CROW + vn * 8) * 2, l0, l1, l2, l3);
-          mma_bf16(st[vn], a0, a1, a2, a3, h0, h1);
-          mma_bf16(st[vn + 1], a0, a1, a2, a3, h2, h3);
-          mma_bf16(st[vn], a0, a1, a2, a3, l0, l1);
-          mma_bf16(st[vn + 1], a0, a1, a2, a3, l2, l3);
+        for (int u = 0; u < CNT / 2; ++u) {
+          ldsm_x4_t(vh_base + (ks * 16 * CROW + u * 16) * 2, hf[u][0], hf[u][1], hf[u][2], hf[u][3]);
+          ldsm_x4_t(vl_base + (ks * 16 * CROW + u * 16) * 2, lf[u][0], lf[u][1], lf[u][2], lf[u][3]);
+        }
+#pragma unroll
+        for (int u = 0; u < CNT / 2; ++u) {
+          mma_bf16(st[2 * u], a0, a1, a2, a3, hf[u][0], hf[u][1]);
+          mma_bf16(st[2 * u + 1], a0, a1, a2, a3, hf[u][2], hf[u][3]);
+        }
+#pragma unroll
+        for (int u = 0; u < CNT / 2; ++u) {
+          mma_bf16(st[2 * u], a0, a1, a2, a3, lf[u][0], lf[u][1]);
+          mma_bf16(st[2 * u + 1], a0, a1, a2, a3, lf[u][2], lf[u][3]);
         }
       }
 #pragma unroll
