@@ -16,6 +16,16 @@
  *                        logarithmic distance bias and an optional sink term in the softmax denominator
  *   pcs_mlstm_gates      capped input / forget gate pre-activations of a matrix-memory recurrent layer
  *   pcs_mlstm_scan       the stabilised matrix-memory recurrence with its per-head output norm and output gate
+ *   pcs_embed_bigram     token embedding plus a row of a hashed (previous token, token) table
+ *   pcs_norm_conv        residual sum, RMS norm (one weight per channel or one number) and a short causal convolution over
+ *                        time whose last inputs are carried in the slot pool
+ *   pcs_rope_kv_prep     rotation of a leading part of every query / key head by position (arbitrary frequency table),
+ *                        unit-RMS values, append of K/V rows to the slot pool
+ *   pcs_moe_route        router of a mixture of experts: softmax scores, choice with a correction and group limits
+ *   pcs_moe_rows_*       the chosen experts' gated feed-forward for a handful of rows (weights streamed once)
+ *   pcs_moe_plan/_gemm   the same for many rows: rows sorted by expert, grouped tensor-core products
+ *   pcs_moe_combine      weighted sum of expert results, pass-through experts and a gated shared expert into the residual
+ *   pcs_silu_mul         silu(gate) * up
  *
  * All tensor arguments are DEVICE pointers; `dtype` selects the compute / storage type of activations, weights and K/V
  * rows: PCS_BF16 or PCS_F32 (true 32-bit everywhere).  The residual stream, norms' statistics, attention scores and
@@ -36,7 +46,7 @@
 extern "C" {
 #endif
 
-#define PCS_ABI_VERSION 1
+#define PCS_ABI_VERSION 2
 #define PCS_BF16 0
 #define PCS_F32 1
 
@@ -119,6 +129,10 @@ typedef struct pcs_attn_params {
   int32_t max_keys;         /* host upper bound of the keys one token sees (sizes the split of the keys); 0: one split */
   float* workspace;         /* fp32 scratch of pcs_attn_workspace_floats() elements, or NULL (one split) */
   int64_t workspace_floats;
+  float softcap;            /* > 0: score = softcap * tanh(score / softcap), after the scale and before the bias */
+  int32_t window;           /* > 0: query i sees key j only if i - j < window or j < keep_first */
+  int32_t keep_first;       /* the first keys of a sequence that stay visible beyond the window */
+  int32_t reserved;
 } pcs_attn_params;
 /* scratch the key split of pcs_attn needs for n_tokens tokens */
 int64_t pcs_attn_workspace_floats(int n_tokens, int n_heads, int vdim);
@@ -160,6 +174,116 @@ typedef struct pcs_mlstm_params {
   int32_t n_tokens, reserved;
 } pcs_mlstm_params;
 int pcs_mlstm_scan(const pcs_mlstm_params* p, void* stream);
+
+/* out[t, :] = table[ids[t], :] + pair[r, :], r = (prev_ids[t] * mul_prev + ids[t] * mul_cur) mod buckets, or r = buckets (the
+ * table's last row) where prev_ids[t] < 0 (a sequence's first token).  out fp32 [n, width]; pair [buckets + 1, width]. */
+int pcs_embed_bigram(const void* table, const void* pair, const int64_t* ids, const int64_t* prev_ids, float* out, int n_tokens,
+                     int width, int vocab, int64_t buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream);
+
+/* Per token t:  x[t] += y_mult * y[t]  (y may be NULL),  u[t] = x[t] / sqrt(mean(x[t]^2) + eps) * g,
+ *               h_out[t] = u[t] + sum_{j < taps} conv_w[:, j] * u[t - taps + 1 + j]        (conv_w NULL: h_out = u)
+ * u of tokens before the sequence's start is zero; u of tokens of earlier steps comes from `tail`, which holds the last
+ * taps - 1 inputs of every slot twice: a step reads copy seq_par[b] and writes copy 1 - seq_par[b] (the caller alternates
+ * seq_par from step to step), so no block reads what another one writes.  y and conv_w together are not supported (the
+ * convolution reads neighbouring rows of x, which other blocks would be updating).  h_out NULL: only the sum. */
+typedef struct pcs_normconv_params {
+  float* x;                 /* [n_tokens, width] */
+  const void* y;            /* [n_tokens, y_stride] `dtype`, or NULL */
+  int64_t y_stride;
+  float y_mult;
+  const void* g;            /* `dtype`: g_len == 1 one number for all channels, else [width] */
+  int32_t g_len;
+  float eps;
+  const void* conv_w;       /* [width, taps] `dtype`, or NULL */
+  int32_t taps;
+  float* tail;              /* [slots, 2, taps - 1, width] fp32 */
+  void* h_out;              /* [n_tokens, width] `dtype`, or NULL */
+  const int32_t* tok_seq;
+  const int32_t* tok_pos;
+  const int32_t* seq_slot;
+  const int32_t* seq_pos0;
+  const int32_t* seq_len;
+  const int32_t* seq_par;
+  int32_t n_tokens, width, dtype, reserved;
+} pcs_normconv_params;
+int pcs_norm_conv(const pcs_normconv_params* p, void* stream);
+
+typedef struct pcs_rope_params {
+  const void* qkv;          /* [n_tokens, row_stride]: q at q_off, k at k_off, v at v_off */
+  int64_t row_stride;
+  int32_t q_off, k_off, v_off;   /* k_off < 0: the layer has no keys and values of its own (it reads another layer's rows) */
+  int32_t n_heads, n_kv_heads, dim, vdim;
+  const double* freqs;      /* [rot_dims / 2] angular frequencies: coordinate pair i of a head turns by pos * freqs[i] */
+  int32_t rot_dims;         /* leading coordinates of every head that are rotated (even, <= dim); the rest pass unchanged */
+  int32_t interleaved;      /* 1: pairs (2i, 2i+1); 0: pairs (i, i + rot_dims/2) */
+  int32_t v_unit_rms;       /* 1: every value head is divided by sqrt(mean(v^2) + eps) before it is cached */
+  float eps;
+  void* q_out;              /* [n_tokens, H*dim] */
+  void* k_pool;             /* [slots, Hkv, cap, dim] */
+  void* v_pool;             /* [slots, Hkv, cap, vdim] */
+  int32_t cap;
+  const int32_t* tok_seq;
+  const int32_t* tok_pos;
+  const int32_t* seq_slot;
+  int32_t n_tokens, dtype;
+} pcs_rope_params;
+int pcs_rope_kv_prep(const pcs_rope_params* p, void* stream);
+
+/* Router of a mixture of experts, per token: z = w_router h (32-bit sums), s = softmax(z) over all n_outputs, choice scores
+ * c = s + correction.  Outputs form n_groups equal groups of neighbours; a group's score is its largest c; only outputs of
+ * the keep_groups best groups can be chosen; the `top` largest c among them are chosen (ties: the lower index).
+ * idx[t, k] = the k-th choice, wgt[t, k] = s of it (not renormalised).  shared_gate[t] = sigmoid(w_sg . h) when w_sg is given. */
+typedef struct pcs_route_params {
+  const void* h;            /* [n_tokens, h_stride] `dtype` */
+  int64_t h_stride;
+  const void* w_router;     /* [n_outputs, width] `dtype` */
+  const float* correction;  /* [n_outputs] or NULL */
+  const void* w_sg;         /* [width] `dtype` or NULL */
+  int32_t n_tokens, width, n_outputs, top, n_groups, keep_groups;
+  int32_t* idx;             /* [n_tokens, top] */
+  float* wgt;               /* [n_tokens, top] */
+  float* shared_gate;       /* [n_tokens] or NULL */
+  int32_t dtype, reserved;
+} pcs_route_params;
+int pcs_moe_route(const pcs_route_params* p, void* stream);
+
+/* The chosen experts for a handful of rows.  Pair p = (token p / top, choice p % top), expert e = idx[p]; e >= n_experts is a
+ * pass-through output and is skipped.  w_gu [n_experts, 2*ff, width] (gate rows, then up rows), w_down [n_experts, width, ff].
+ *   pcs_moe_rows_up:    act[p, :] = silu(W_gate_e h) * (W_up_e h)        act `dtype` [pairs, ff]
+ *   pcs_moe_rows_down:  y[p, :]  = W_down_e act[p, :]                    y fp32 [pairs, width] */
+int pcs_moe_rows_up(const void* h, int64_t h_stride, const void* w_gu, const int32_t* idx, void* act, int n_pairs, int top, int n_experts,
+                    int ff, int width, int dtype, void* stream);
+int pcs_moe_rows_down(const void* act, const void* w_down, const int32_t* idx, float* y, int n_pairs, int n_experts, int ff, int width,
+                      int dtype, void* stream);
+
+/* Many rows: pairs are sorted by expert on the device.  `plan` is int32 scratch of pcs_moe_plan_ints(n_pairs, n_experts)
+ * elements: [0] number of row tiles, then per tile (expert, first sorted row, rows), then the sorted pair list. */
+int64_t pcs_moe_plan_ints(int n_pairs, int n_experts);
+int pcs_moe_plan(const int32_t* idx, int n_pairs, int n_experts, int32_t* plan, void* stream);
+/* stage 0: act[sorted row, :] = silu(W_gate_e h[pair / top]) * (W_up_e h[pair / top])   (bf16 [n_pairs, ff])
+ * stage 1: y[pair, :] = W_down_e act[sorted row, :]                                      (fp32 [n_pairs, width])
+ * bfloat16 only; ff and width multiples of 8. */
+int pcs_moe_gemm(int stage, const void* a, int64_t a_stride, const void* w, const int32_t* plan, void* out, int n_pairs, int top,
+                 int n_experts, int ff, int width, void* stream);
+
+/* x[t] += mult * ( sum_k wgt[t,k] * (idx[t,k] < n_experts ? y[t*top + k] : h[t]) + (ys ? shared_gate[t] * ys[t] : 0) ) */
+typedef struct pcs_combine_params {
+  float* x;                 /* [n_tokens, width] */
+  const float* y;           /* [n_tokens * top, width] */
+  const int32_t* idx;
+  const float* wgt;
+  const void* h;            /* [n_tokens, h_stride] `dtype`: what pass-through outputs hand on */
+  int64_t h_stride;
+  const void* ys;           /* [n_tokens, ys_stride] `dtype` or NULL: the shared expert's result */
+  int64_t ys_stride;
+  const float* shared_gate; /* [n_tokens] or NULL (ys is added as it is) */
+  float mult;
+  int32_t n_tokens, width, top, n_experts, dtype, reserved;
+} pcs_combine_params;
+int pcs_moe_combine(const pcs_combine_params* p, void* stream);
+
+/* out[r, c] = silu(gu[r, c]) * gu[r, ff + c]     (gu `dtype` [n_rows, gu_stride], out `dtype` [n_rows, ff]) */
+int pcs_silu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -17,7 +17,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libpromptcache_b200_seq.so")
 PCS_BF16, PCS_F32 = 0, 1
 EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_attn_workspace_floats", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu", "pcs_linear_rows",
-           "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan")
+           "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan", "pcs_embed_bigram", "pcs_norm_conv", "pcs_rope_kv_prep", "pcs_moe_route",
+           "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul")
 
 
 class pcs_gna_params(C.Structure):
@@ -44,7 +45,37 @@ class pcs_attn_params(C.Structure):
                 ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p),
                 ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
                 ("n_tokens", C.c_int32), ("n_seqs", C.c_int32), ("max_len", C.c_int32), ("dtype", C.c_int32),
-                ("impl", C.c_int32), ("max_keys", C.c_int32), ("workspace", C.c_void_p), ("workspace_floats", C.c_int64)]
+                ("impl", C.c_int32), ("max_keys", C.c_int32), ("workspace", C.c_void_p), ("workspace_floats", C.c_int64),
+                ("softcap", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("reserved", C.c_int32)]
+
+
+class pcs_normconv_params(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("y_stride", C.c_int64), ("y_mult", C.c_float), ("g", C.c_void_p), ("g_len", C.c_int32),
+                ("eps", C.c_float), ("conv_w", C.c_void_p), ("taps", C.c_int32), ("tail", C.c_void_p), ("h_out", C.c_void_p),
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p), ("seq_len", C.c_void_p),
+                ("seq_par", C.c_void_p), ("n_tokens", C.c_int32), ("width", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
+class pcs_rope_params(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("row_stride", C.c_int64), ("q_off", C.c_int32), ("k_off", C.c_int32), ("v_off", C.c_int32),
+                ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
+                ("freqs", C.c_void_p), ("rot_dims", C.c_int32), ("interleaved", C.c_int32), ("v_unit_rms", C.c_int32), ("eps", C.c_float),
+                ("q_out", C.c_void_p), ("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("cap", C.c_int32),
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("n_tokens", C.c_int32), ("dtype", C.c_int32)]
+
+
+class pcs_route_params(C.Structure):
+    _fields_ = [("h", C.c_void_p), ("h_stride", C.c_int64), ("w_router", C.c_void_p), ("correction", C.c_void_p), ("w_sg", C.c_void_p),
+                ("n_tokens", C.c_int32), ("width", C.c_int32), ("n_outputs", C.c_int32), ("top", C.c_int32), ("n_groups", C.c_int32),
+                ("keep_groups", C.c_int32), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("shared_gate", C.c_void_p),
+                ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
+class pcs_combine_params(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("h", C.c_void_p), ("h_stride", C.c_int64),
+                ("ys", C.c_void_p), ("ys_stride", C.c_int64), ("shared_gate", C.c_void_p), ("mult", C.c_float),
+                ("n_tokens", C.c_int32), ("width", C.c_int32), ("top", C.c_int32), ("n_experts", C.c_int32), ("dtype", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 class pcs_mlstm_params(C.Structure):
@@ -89,6 +120,22 @@ def load() -> C.CDLL:
     lib.pcs_mlstm_scan.argtypes = [C.POINTER(pcs_mlstm_params), C.c_void_p]
     lib.pcs_attn_workspace_floats.argtypes = [C.c_int, C.c_int, C.c_int]
     lib.pcs_attn_workspace_floats.restype = C.c_int64
+    lib.pcs_embed_bigram.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64,
+                                     C.c_int64, C.c_int, C.c_void_p]
+    lib.pcs_norm_conv.argtypes = [C.POINTER(pcs_normconv_params), C.c_void_p]
+    lib.pcs_rope_kv_prep.argtypes = [C.POINTER(pcs_rope_params), C.c_void_p]
+    lib.pcs_moe_route.argtypes = [C.POINTER(pcs_route_params), C.c_void_p]
+    lib.pcs_moe_rows_up.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                    C.c_void_p]
+    lib.pcs_moe_rows_down.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    # (the grouped products are declared below)
+    lib.pcs_moe_plan_ints.argtypes = [C.c_int, C.c_int]
+    lib.pcs_moe_plan_ints.restype = C.c_int64
+    lib.pcs_moe_plan.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.pcs_moe_gemm.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                 C.c_void_p]
+    lib.pcs_moe_combine.argtypes = [C.POINTER(pcs_combine_params), C.c_void_p]
+    lib.pcs_silu_mul.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     for name in EXPORTS[4:]:
         getattr(lib, name).restype = C.c_int
     _lib = lib
@@ -133,22 +180,25 @@ def launch_count() -> int:
 
 class Batch:
     """The int32 description of one step's batch on the device (one host-to-device copy): per token its entry and position,
-    per entry its slot, the tokens the slot already holds, the number of new tokens and the index of the first one."""
+    per entry its slot, the tokens the slot already holds, the number of new tokens, the index of the first one and the
+    parity of the sequence's step count (which of two copies of a double-buffered state the step reads)."""
 
-    def __init__(self, slots, pos0, lens, device):
+    def __init__(self, slots, pos0, lens, device, parity=None):
         n_seqs, n_tokens = len(slots), int(sum(lens))
+        parity = list(parity) if parity is not None else [0] * n_seqs
         offs, tok_seq, tok_pos, o = [], [], [], 0
         for b, (p0, n) in enumerate(zip(pos0, lens)):
             offs.append(o)
             tok_seq += [b] * n
             tok_pos += range(p0, p0 + n)
             o += n
-        host = torch.tensor(tok_seq + tok_pos + list(slots) + list(pos0) + list(lens) + offs, dtype=torch.int32)
+        host = torch.tensor(tok_seq + tok_pos + list(slots) + list(pos0) + list(lens) + offs + parity, dtype=torch.int32)
         self.meta = host.pin_memory().to(device, non_blocking=True) if device.type == "cuda" else host
         T, B = n_tokens, n_seqs
         m = self.meta
         self.tok_seq, self.tok_pos = m[0:T], m[T:2 * T]
-        self.seq_slot, self.seq_pos0, self.seq_len, self.seq_off = (m[2 * T + i * B:2 * T + (i + 1) * B] for i in range(4))
+        self.seq_slot, self.seq_pos0, self.seq_len, self.seq_off, self.seq_par = (m[2 * T + i * B:2 * T + (i + 1) * B] for i in range(5))
+        self.prev_ids = None  # int64 [T] on the device: every token's predecessor in its sequence, -1 for a first token
         self.n_tokens, self.n_seqs, self.max_len = T, B, max(lens) if lens else 0
         self.offsets, self.lens, self.pos0, self.slots = offs, list(lens), list(pos0), list(slots)
 
@@ -250,10 +300,12 @@ def qk_prep(qkv: torch.Tensor, offs, q_norm_w, k_norm_w, eps: float, n_heads: in
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float,
               r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: bool, batch: Batch, impl: int = 0,
-              max_keys: int = 0, workspace: Optional[torch.Tensor] = None) -> None:
+              max_keys: int = 0, workspace: Optional[torch.Tensor] = None, softcap: float = 0.0, window: int = 0,
+              keep_first: int = 0) -> None:
     """q [T, H*dim], out [T, H*vdim]; causal over each entry's own slot rows; r1 / r2 float32 [H] or None.  With a float32
     `workspace` (attn_workspace) and `max_keys` (upper bound of the keys a token sees) few tokens over many keys are run
-    as several splits of the keys that a second launch merges."""
+    as several splits of the keys that a second launch merges.  `softcap` > 0 caps the scaled score by softcap * tanh(s /
+    softcap); `window` > 0 limits query i to keys j with i - j < window or j < keep_first."""
     _cuda(q, k_pool, v_pool, out, r1, r2)
     dt = q.dtype
     if not (q.is_contiguous() and out.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous()) or out.dtype != dt \
@@ -269,6 +321,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
     p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
     p.seq_pos0, p.seq_len, p.seq_off = batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(), batch.seq_off.data_ptr()
     p.n_tokens, p.n_seqs, p.max_len, p.dtype, p.impl = batch.n_tokens, batch.n_seqs, batch.max_len, dtype_code(dt), impl
+    p.softcap, p.window, p.keep_first = float(softcap), int(window), int(keep_first)
     if workspace is not None:
         if workspace.dtype != torch.float32 or not workspace.is_cuda or not workspace.is_contiguous():
             raise NativeError("attention: the workspace must be a contiguous CUDA float32 tensor")
@@ -316,3 +369,169 @@ def mlstm_scan(proj: torch.Tensor, offs, ig: torch.Tensor, fg: torch.Tensor, nor
     o_raw = torch.empty(batch.n_tokens * p.heads * p.vdim + batch.n_seqs * p.heads * (p.dim + 1), dtype=torch.float32, device=proj.device)
     p.o_raw, p.n_tokens = o_raw.data_ptr(), batch.n_tokens
     _check(load().pcs_mlstm_scan(C.byref(p), _stream()), "pcs_mlstm_scan")
+
+
+def embed_bigram(table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, prev_ids: torch.Tensor, out: torch.Tensor, buckets: int,
+                 mul_prev: int, mul_cur: int) -> None:
+    """out = table[ids] + pair[(prev * mul_prev + id * mul_cur) mod buckets], the pair table's last row where prev < 0."""
+    _cuda(table, pair, ids, prev_ids, out)
+    if ids.dtype != torch.int64 or prev_ids.dtype != torch.int64 or not ids.is_contiguous() or not prev_ids.is_contiguous() \
+            or prev_ids.numel() != ids.numel() or out.dtype != torch.float32 or not out.is_contiguous():
+        raise NativeError("embed_bigram: ids and prev_ids contiguous int64 of one length, out contiguous float32")
+    if not (table.is_contiguous() and pair.is_contiguous()) or pair.dtype != table.dtype or pair.shape[0] != buckets + 1 or pair.shape[1] != table.shape[1]:
+        raise NativeError("embed_bigram: the pair table must be [buckets + 1, width] in the embedding's type")
+    _check(load().pcs_embed_bigram(table.data_ptr(), pair.data_ptr(), ids.data_ptr(), prev_ids.data_ptr(), out.data_ptr(), ids.numel(),
+                                   table.shape[1], table.shape[0], int(buckets), int(mul_prev), int(mul_cur), dtype_code(table.dtype), _stream()),
+           "pcs_embed_bigram")
+
+
+def norm_conv(x: torch.Tensor, g: Optional[torch.Tensor], eps: float, h_out: Optional[torch.Tensor], y: Optional[torch.Tensor] = None,
+              y_mult: float = 1.0, conv_w: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None, batch: Optional[Batch] = None) -> None:
+    """x += y_mult * y (when y is given); h_out = u + causal_conv(u) with u = rms_norm(x) * g (g: one number or [width]).  `tail`
+    [slots, 2, taps - 1, width] float32 carries the last inputs of every slot from step to step."""
+    _cuda(x, g, h_out, y, conv_w, tail)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
+        raise NativeError("norm_conv: x must be a contiguous float32 matrix")
+    dt = h_out.dtype if h_out is not None else y.dtype
+    p = pcs_normconv_params()
+    p.x, p.eps, p.n_tokens, p.width, p.dtype = x.data_ptr(), float(eps), x.shape[0], x.shape[1], dtype_code(dt)
+    if y is not None:
+        _rows2d(y, dt, "norm_conv: y")
+        if y.shape != x.shape:
+            raise NativeError("norm_conv: y must have x's shape")
+        p.y, p.y_stride, p.y_mult = y.data_ptr(), y.stride(0), float(y_mult)
+    if h_out is not None:
+        if g is None or g.dtype != dt or not g.is_contiguous() or g.numel() not in (1, x.shape[1]) or not h_out.is_contiguous() or h_out.shape != x.shape:
+            raise NativeError("norm_conv: g is one number or [width] in h_out's type; h_out contiguous of x's shape")
+        p.g, p.g_len, p.h_out = g.data_ptr(), g.numel(), h_out.data_ptr()
+    if conv_w is not None:
+        taps = conv_w.shape[1]
+        if conv_w.dtype != dt or not conv_w.is_contiguous() or conv_w.shape[0] != x.shape[1] or batch is None:
+            raise NativeError("norm_conv: conv_w must be contiguous [width, taps] in the compute type, with the batch given")
+        if taps > 1 and (tail is None or tail.dtype != torch.float32 or not tail.is_contiguous() or tuple(tail.shape[1:]) != (2, taps - 1, x.shape[1])):
+            raise NativeError("norm_conv: tail must be contiguous float32 [slots, 2, taps - 1, width]")
+        p.conv_w, p.taps, p.tail = conv_w.data_ptr(), taps, _ptr(tail)
+        p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
+        p.seq_pos0, p.seq_len, p.seq_par = batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(), batch.seq_par.data_ptr()
+    _check(load().pcs_norm_conv(C.byref(p), _stream()), "pcs_norm_conv")
+
+
+def rope_kv_prep(qkv: torch.Tensor, offs, n_heads: int, n_kv_heads: int, dim: int, vdim: int, freqs: Optional[torch.Tensor], rot_dims: int,
+                 interleaved: bool, v_unit_rms: bool, eps: float, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
+                 v_pool: Optional[torch.Tensor], batch: Batch) -> None:
+    """qkv [T, *] with q / k / v at the column offsets `offs` (k and v offsets None: the layer appends no rows).  freqs: float64
+    [rot_dims / 2] on the device."""
+    _cuda(qkv, q_out, k_pool, v_pool, freqs)
+    dt = qkv.dtype
+    _rows2d(qkv, dt, "rope_kv_prep: qkv")
+    if not q_out.is_contiguous() or q_out.dtype != dt:
+        raise NativeError("rope_kv_prep: q_out must be contiguous in the compute type")
+    if freqs is not None and (freqs.dtype != torch.float64 or not freqs.is_contiguous() or freqs.numel() < rot_dims // 2):
+        raise NativeError("rope_kv_prep: freqs must be contiguous float64 [rot_dims / 2]")
+    p = pcs_rope_params()
+    p.qkv, p.row_stride = qkv.data_ptr(), qkv.stride(0)
+    p.q_off, p.k_off, p.v_off = offs[0], -1 if offs[1] is None else offs[1], -1 if offs[2] is None else offs[2]
+    p.n_heads, p.n_kv_heads, p.dim, p.vdim = n_heads, n_kv_heads, dim, vdim
+    p.freqs, p.rot_dims, p.interleaved, p.v_unit_rms, p.eps = _ptr(freqs), int(rot_dims), 1 if interleaved else 0, 1 if v_unit_rms else 0, float(eps)
+    p.q_out = q_out.data_ptr()
+    if offs[1] is not None:
+        if k_pool is None or v_pool is None or not (k_pool.is_contiguous() and v_pool.is_contiguous()) or k_pool.dtype != dt or v_pool.dtype != dt \
+                or tuple(k_pool.shape[1:]) != (n_kv_heads, k_pool.shape[2], dim) or tuple(v_pool.shape[1:]) != (n_kv_heads, k_pool.shape[2], vdim):
+            raise NativeError("rope_kv_prep: pools must be contiguous [slots, Hkv, cap, dim | vdim] in the compute type")
+        p.k_pool, p.v_pool, p.cap = k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[2]
+    p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
+    p.n_tokens, p.dtype = batch.n_tokens, dtype_code(dt)
+    _check(load().pcs_rope_kv_prep(C.byref(p), _stream()), "pcs_rope_kv_prep")
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], w_sg: Optional[torch.Tensor], top: int, n_groups: int,
+              keep_groups: int):
+    """(idx int32 [T, top], wgt float32 [T, top], shared gate float32 [T] or None)."""
+    _cuda(h, w_router, correction, w_sg)
+    dt = h.dtype
+    _rows2d(h, dt, "moe_route: h")
+    if w_router.dtype != dt or not w_router.is_contiguous() or w_router.shape[1] != h.shape[1]:
+        raise NativeError("moe_route: the router matrix must be contiguous [outputs, width] in h's type")
+    if correction is not None and (correction.dtype != torch.float32 or not correction.is_contiguous() or correction.numel() != w_router.shape[0]):
+        raise NativeError("moe_route: correction must be float32 [outputs]")
+    if w_sg is not None and (w_sg.dtype != dt or not w_sg.is_contiguous() or w_sg.numel() != h.shape[1]):
+        raise NativeError("moe_route: the shared gate's weights must be [width] in h's type")
+    T = h.shape[0]
+    idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
+    wgt = torch.empty(T, top, dtype=torch.float32, device=h.device)
+    sg = torch.empty(T, dtype=torch.float32, device=h.device) if w_sg is not None else None
+    p = pcs_route_params()
+    p.h, p.h_stride, p.w_router, p.correction, p.w_sg = h.data_ptr(), h.stride(0), w_router.data_ptr(), _ptr(correction), _ptr(w_sg)
+    p.n_tokens, p.width, p.n_outputs, p.top, p.n_groups, p.keep_groups = T, h.shape[1], w_router.shape[0], int(top), int(n_groups), int(keep_groups)
+    p.idx, p.wgt, p.shared_gate, p.dtype = idx.data_ptr(), wgt.data_ptr(), _ptr(sg), dtype_code(dt)
+    _check(load().pcs_moe_route(C.byref(p), _stream()), "pcs_moe_route")
+    return idx, wgt, sg
+
+
+MOE_ROWS_MAX_PAIRS = 64
+
+
+def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, grouped: Optional[bool] = None) -> torch.Tensor:
+    """The chosen experts' results, float32 [T * top, width] (rows of pass-through choices are not written).  w_gu [E, 2 ff,
+    width], w_down [E, width, ff].  Few pairs stream each chosen expert's weights once; many pairs in bfloat16 are sorted
+    by expert and go through the grouped tensor-core products."""
+    _cuda(h, idx, w_gu, w_down)
+    dt = h.dtype
+    _rows2d(h, dt, "moe_experts: h")
+    E, ff2, W = w_gu.shape
+    ff = ff2 // 2
+    if w_gu.dtype != dt or w_down.dtype != dt or not (w_gu.is_contiguous() and w_down.is_contiguous()) or tuple(w_down.shape) != (E, W, ff) \
+            or idx.dtype != torch.int32 or not idx.is_contiguous() or W != h.shape[1]:
+        raise NativeError("moe_experts: weights [E, 2 ff, width] and [E, width, ff] in h's type, idx contiguous int32")
+    T, top = idx.shape
+    P = T * top
+    y = torch.empty(P, W, dtype=torch.float32, device=h.device)
+    act = torch.empty(P, ff, dtype=dt, device=h.device)
+    can_group = dt == torch.bfloat16 and ff % 8 == 0 and W % 8 == 0 and (h.stride(0) * 2) % 16 == 0 and h.data_ptr() % 16 == 0
+    if grouped is None:
+        grouped = can_group and P > MOE_ROWS_MAX_PAIRS
+    if grouped:
+        if not can_group:
+            raise NativeError("moe_experts: the grouped products need bfloat16 and sizes that are multiples of 8")
+        lib = load()
+        plan = torch.empty(int(lib.pcs_moe_plan_ints(P, E)), dtype=torch.int32, device=h.device)
+        _check(lib.pcs_moe_plan(idx.data_ptr(), P, E, plan.data_ptr(), _stream()), "pcs_moe_plan")
+        _check(lib.pcs_moe_gemm(0, h.data_ptr(), h.stride(0), w_gu.data_ptr(), plan.data_ptr(), act.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
+        _check(lib.pcs_moe_gemm(1, act.data_ptr(), ff, w_down.data_ptr(), plan.data_ptr(), y.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
+        return y
+    _check(load().pcs_moe_rows_up(h.data_ptr(), h.stride(0), w_gu.data_ptr(), idx.data_ptr(), act.data_ptr(), P, top, E, ff, W, dtype_code(dt), _stream()),
+           "pcs_moe_rows_up")
+    _check(load().pcs_moe_rows_down(act.data_ptr(), w_down.data_ptr(), idx.data_ptr(), y.data_ptr(), P, E, ff, W, dtype_code(dt), _stream()),
+           "pcs_moe_rows_down")
+    return y
+
+
+def moe_combine(x: torch.Tensor, y: Optional[torch.Tensor], idx: torch.Tensor, wgt: torch.Tensor, h: torch.Tensor, n_experts: int, mult: float,
+                ys: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
+    """x += mult * (sum_k wgt[:, k] * (y of the choice, or h itself for a choice >= n_experts) + shared_gate * ys)."""
+    _cuda(x, y, idx, wgt, h, ys, shared_gate)
+    dt = h.dtype
+    _rows2d(h, dt, "moe_combine: h")
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.shape != h.shape:
+        raise NativeError("moe_combine: x must be contiguous float32 of h's shape")
+    T, top = idx.shape
+    if idx.dtype != torch.int32 or wgt.dtype != torch.float32 or not (idx.is_contiguous() and wgt.is_contiguous()) or wgt.shape != idx.shape or T != x.shape[0]:
+        raise NativeError("moe_combine: idx int32 and wgt float32 [T, top]")
+    if y is not None and (y.dtype != torch.float32 or not y.is_contiguous() or tuple(y.shape) != (T * top, x.shape[1])):
+        raise NativeError("moe_combine: y must be contiguous float32 [T * top, width]")
+    if ys is not None:
+        _rows2d(ys, dt, "moe_combine: ys")
+    p = pcs_combine_params()
+    p.x, p.y, p.idx, p.wgt, p.h, p.h_stride = x.data_ptr(), _ptr(y), idx.data_ptr(), wgt.data_ptr(), h.data_ptr(), h.stride(0)
+    p.ys, p.ys_stride, p.shared_gate, p.mult = _ptr(ys), ys.stride(0) if ys is not None else 0, _ptr(shared_gate), float(mult)
+    p.n_tokens, p.width, p.top, p.n_experts, p.dtype = T, x.shape[1], top, int(n_experts), dtype_code(dt)
+    _check(load().pcs_moe_combine(C.byref(p), _stream()), "pcs_moe_combine")
+
+
+def silu_mul(gu: torch.Tensor, ff: int) -> torch.Tensor:
+    """silu(gu[:, :ff]) * gu[:, ff:2 ff]."""
+    _cuda(gu)
+    _rows2d(gu, gu.dtype, "silu_mul: gu")
+    out = torch.empty(gu.shape[0], ff, dtype=gu.dtype, device=gu.device)
+    _check(load().pcs_silu_mul(gu.data_ptr(), gu.stride(0), out.data_ptr(), gu.shape[0], ff, dtype_code(gu.dtype), _stream()), "pcs_silu_mul")
+    return out

@@ -6,7 +6,9 @@
 // pcs_attn      one block per (token, head, split of the keys): keys in tiles of 128, one key per thread for the score, online softmax in
 //               32-bit, then one value column per thread.  Scores, weights and the accumulator are 32-bit in both types.
 //               A sink is one more term exp(0 - m) of the denominator that has no value: the running maximum starts at 0
-//               and the running sum at 1 instead of (-inf, 0).
+//               and the running sum at 1 instead of (-inf, 0).  A score may be capped (cap * tanh(score / cap)), and the keys may
+//               be limited to a sliding window plus the first keys of the sequence: a query then walks a dense list of its
+//               visible keys, so its work is bounded by window + keep_first whatever the sequence's length.
 #include "seq_common.cuh"
 
 namespace pcs {
@@ -174,6 +176,18 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(const pcs_qkprep_param
 constexpr int kAttnThreads = 128;
 constexpr int kAttnMaxVPT = 4;  // value columns per thread: vdim <= 512
 
+// The keys a query at position `pos` sees, as one dense index range: with a window, the kept first keys [0, n_first) and
+// then the window [lo, pos]; without one (or when the two touch), all of [0, pos].
+struct VisibleKeys {
+  int n_first, lo, count;
+  __device__ __forceinline__ VisibleKeys(int pos, int window, int keep_first) {
+    lo = window > 0 ? max(0, pos - window + 1) : 0;
+    n_first = min(max(keep_first, 0), lo);
+    count = n_first + (pos + 1 - lo);
+  }
+  __device__ __forceinline__ int key(int v) const { return v < n_first ? v : lo + (v - n_first); }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn_params p) {
   extern __shared__ float sm[];  // q[dim], w[128]
@@ -190,7 +204,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
   const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
   // keys are cut into gridDim.z splits of whole tiles; the sink belongs to split 0
-  const int n_keys = pos + 1, S = gridDim.z, sp = blockIdx.z;
+  const VisibleKeys vis(pos, p.window, p.keep_first);
+  const int n_keys = vis.count, S = gridDim.z, sp = blockIdx.z;
   const int chunk = ((n_keys + S - 1) / S + kAttnThreads - 1) / kAttnThreads * kAttnThreads;
   const int k_begin = sp * chunk, k_end = min(n_keys, k_begin + chunk);
   const bool sink_here = p.sink && sp == 0;
@@ -199,9 +214,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   const bool vec = (D % Vec<T>::n) == 0;
   __syncthreads();
   for (int j0 = k_begin; j0 < k_end; j0 += kAttnThreads) {
-    const int j = j0 + tid;
+    const int j = vis.key(j0 + tid);
     float s = -INFINITY;
-    if (j < k_end) {
+    if (j0 + tid < k_end) {
       const T* kr = K + static_cast<long long>(j) * D;
       float a = 0.f;
       if (vec) {
@@ -215,12 +230,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
         for (int d = 0; d < D; ++d) a = fmaf(qs[d], ldf(kr + d), a);
       }
       s = a * p.scale;
+      if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
       if (p.bias_r1) s -= r1 * log1pf(r2 * static_cast<float>(pos - j));
     }
     const float tmax = block_max(s, red);
     const float m_new = fmaxf(m, tmax);
     const float f = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    const float w = (j < k_end) ? expf(s - m_new) : 0.f;
+    const float w = (j0 + tid < k_end) ? expf(s - m_new) : 0.f;
     ws[tid] = w;
     const float tsum = block_sum(w, red);  // its barriers also publish ws
     l = l * f + tsum;
@@ -231,8 +247,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
       const int c = tid + u * kAttnThreads;
       if (c < V) {
         float a = acc[u] * f;
-        const T* vr = Vp + static_cast<long long>(j0) * V + c;
-        for (int jj = 0; jj < nt; ++jj) a = fmaf(ws[jj], ldf(vr + static_cast<long long>(jj) * V), a);
+        for (int jj = 0; jj < nt; ++jj) a = fmaf(ws[jj], ldf(Vp + static_cast<long long>(vis.key(j0 + jj)) * V + c), a);
         acc[u] = a;
       }
     }
@@ -281,7 +296,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
   const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
   for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
   const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
-  const int n_keys = pos + 1, S = gridDim.z, sp = blockIdx.z;
+  const VisibleKeys vis(pos, p.window, p.keep_first);
+  const int n_keys = vis.count, S = gridDim.z, sp = blockIdx.z;
   const int chunk = ((n_keys + S - 1) / S + kAttnThreads - 1) / kAttnThreads * kAttnThreads;
   const int k_begin = sp * chunk, k_end = min(n_keys, k_begin + chunk);
   const bool sink_here = p.sink && sp == 0;
@@ -295,9 +311,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
   for (int e = 0; e < N; ++e) acc[e] = 0.f;
   __syncthreads();
   for (int j0 = k_begin; j0 < k_end; j0 += kAttnThreads) {
-    const int j = j0 + tid;
+    const int j = vis.key(j0 + tid);
     float s = -INFINITY;
-    if (j < k_end) {
+    if (j0 + tid < k_end) {
       const T* kr = K + static_cast<long long>(j) * D;
       float a0 = 0.f, a1 = 0.f;
       int d = 0;
@@ -322,6 +338,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
         for (int e = 0; e < N; ++e) a0 = fmaf(qs[d + e], k0[e], a0);
       }
       s = (a0 + a1) * p.scale;
+      if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
       if (p.bias_r1) s -= r1 * log1pf(r2 * static_cast<float>(pos - j));
     }
     const float wm = warp_max(s);
@@ -333,21 +350,21 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
     const float m_new = fmaxf(m, tmax);  // finite: a tile has at least one key
     const float f = (m == -INFINITY) ? 0.f : expf(m - m_new);
     m = m_new;
-    ws[tid] = (j < k_end) ? expf(s - m_new) : 0.f;
+    ws[tid] = (j0 + tid < k_end) ? expf(s - m_new) : 0.f;
     __syncthreads();
     if (active) {
       const int nt = min(kAttnThreads, k_end - j0);
       lsum *= f;
 #pragma unroll
       for (int e = 0; e < N; ++e) acc[e] *= f;
-      const T* vr = Vp + static_cast<long long>(j0) * V + c * N;
+      const T* vr = Vp + c * N;
       int jj = r;
       for (; jj + 3 * R < nt; jj += 4 * R) {
         float v0[N], v1[N], v2[N], v3[N];
-        ld16(vr + static_cast<long long>(jj) * V, v0);
-        ld16(vr + static_cast<long long>(jj + R) * V, v1);
-        ld16(vr + static_cast<long long>(jj + 2 * R) * V, v2);
-        ld16(vr + static_cast<long long>(jj + 3 * R) * V, v3);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * V, v0);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj + R)) * V, v1);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj + 2 * R)) * V, v2);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj + 3 * R)) * V, v3);
         const float w0 = ws[jj], w1 = ws[jj + R], w2 = ws[jj + 2 * R], w3 = ws[jj + 3 * R];
 #pragma unroll
         for (int e = 0; e < N; ++e) acc[e] = fmaf(w3, v3[e], fmaf(w2, v2[e], fmaf(w1, v1[e], fmaf(w0, v0[e], acc[e]))));
@@ -355,7 +372,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
       }
       for (; jj < nt; jj += R) {
         float v0[N];
-        ld16(vr + static_cast<long long>(jj) * V, v0);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * V, v0);
         const float w0 = ws[jj];
 #pragma unroll
         for (int e = 0; e < N; ++e) acc[e] = fmaf(w0, v0[e], acc[e]);

@@ -262,6 +262,7 @@ int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled) {
   *handled = false;
   if (p.dtype != PCS_BF16 || p.max_len < 16 || p.dim % 8 != 0 || p.vdim % 8 != 0 || p.dim > 256 || p.vdim > 256) return PCS_OK;
   if (!p.seq_pos0 || !p.seq_len || !p.seq_off) return PCS_OK;
+  if (p.window > 0 || p.softcap > 0.f) return PCS_OK;
   if (static_cast<long long>((p.max_len + BM - 1) / BM) * p.n_seqs * p.n_heads > 0x7fffffffLL) return PCS_OK;
   *handled = true;
   if (p.dim <= 64) return launch_v<64>(p, st);

@@ -216,9 +216,31 @@ class Mutolix(LanguageModel):
         raise NotImplementedError("Mutolix keeps recurrent state next to K/V rows: there is no per-module K/V to cache and splice")
 
 
+class Raritar(LanguageModel):
+    """Adapter of the Raritar design (model/raritar.py) for the generation engine.  Its embedding looks at the previous token
+    and its layers carry a short convolution's inputs, so a prompt's state cannot be cut at module boundaries and spliced:
+    pass `cache=None` to `GenerationEngine.generate`, or batch requests with `BatchEngine`."""
+
+    def __init__(self, name: str, model=None, tokenizer=None, **kwargs):
+        from .raritar import RaritarForCausalLM
+        if model is None:
+            model = RaritarForCausalLM.from_pretrained(name, **kwargs)
+        if tokenizer is None:
+            from ..synthetic import IdTokenizer
+            tokenizer = IdTokenizer(model.vocab_size)
+        super().__init__(name, model, tokenizer, [tokenizer.eos_token_id], [])
+
+    def get_formatter(self) -> Callable[[str], str]:
+        return lambda prompt: prompt
+
+    def get_cache_shape(self) -> Tuple[int, int, int]:
+        raise NotImplementedError("Raritar keeps per-sequence state beside its K/V rows: there is no per-module K/V to cache and splice")
+
+
 # config.json "architecture" (or transformers' "architectures"/"model_type") -> loader of the bare model
 MODEL_REGISTRY = {
     "Mutolix": lambda path, **kw: _mutolix(path, **kw),
+    "Raritar": lambda path, **kw: _lazy("raritar", "RaritarForCausalLM").from_pretrained(path, **kw),
     "LlamaForCausalLM": lambda path, dtype=None, **kw: LlamaForCausalLM.from_pretrained(path, **kw),
     "FalconForCausalLM": lambda path, dtype=None, **kw: _lazy("falcon", "FalconForCausalLM").from_pretrained(path, **kw),
     "MptForCausalLM": lambda path, dtype=None, **kw: _lazy("mpt", "MptForCausalLM").from_pretrained(path, **kw),
@@ -250,5 +272,5 @@ def load_model(path: str, device="cuda", dtype=None, **kwargs):
     return loader(path, device=device, **kwargs)
 
 
-__all__ = ["LanguageModel", "Mutolix", "MODEL_REGISTRY", "load_model", "Llama2", "CodeLlama", "Falcon", "Mpt", "FormatConversation",
+__all__ = ["LanguageModel", "Mutolix", "Raritar", "MODEL_REGISTRY", "load_model", "Llama2", "CodeLlama", "Falcon", "Mpt", "FormatConversation",
            "FormatLlama2Conversation", "LlamaForCausalLM", "LlamaConfigLite"]

@@ -73,20 +73,27 @@ class SlotPoolCausalLM(nn.Module):
                 rows.append(off + i)
             off += n
         flat = [int(t) for _, toks in entries for t in toks]
+        prev = []   # every token's predecessor in its own sequence (-1: none)
+        for seq, toks in entries:
+            prev += [seq.last_token if seq.rows > 0 else -1] + [int(t) for t in list(toks)[:-1]]
+        parity = [s.steps & 1 for s, _ in entries]
         decode = max(lens) == 1 and min(pos0) > 0 and len(rows) == len(entries)
         logits = None
         if decode and self.use_cuda_graphs and not torch.cuda.is_current_stream_capturing():
-            logits = self._decode_replay(flat, slots, pos0)
+            logits = self._decode_replay(flat, slots, pos0, prev, parity)
         if logits is None:
-            batch = nsq.Batch(slots, pos0, lens, self._device)
-            ids = torch.tensor(flat, dtype=torch.int64).pin_memory().to(self._device, non_blocking=True)
+            batch = nsq.Batch(slots, pos0, lens, self._device, parity)
+            both = torch.tensor(flat + prev, dtype=torch.int64).pin_memory().to(self._device, non_blocking=True)
+            ids, batch.prev_ids = both[:len(flat)], both[len(flat):]
             rows_t = torch.tensor(rows, dtype=torch.int32).pin_memory().to(self._device, non_blocking=True) if rows else None
             logits = self._layers(ids, batch, rows_t)
-        for (seq, _), n in zip(entries, lens):
+        for (seq, toks), n in zip(entries, lens):
             self.pool.rows[seq.slot] += n
+            seq.steps += 1
+            seq.last_token = int(toks[-1])
         return logits
 
-    def _decode_replay(self, flat, slots, pos0):
+    def _decode_replay(self, flat, slots, pos0, prev, parity):
         """One-token-per-sequence steps of a given batch size replay ONE captured graph: everything that changes from step
         to step (token ids, slots, positions) lives in static device buffers the kernels read at run time."""
         B = len(flat)
@@ -98,8 +105,9 @@ class SlotPoolCausalLM(nn.Module):
                 return None  # the first such step runs eagerly (it also warms up the libraries' workspaces)
             if len(self._graphs) >= self.max_graphs:
                 self._graphs.pop(next(iter(self._graphs)))
-            batch = nsq.Batch(slots, pos0, [1] * B, self._device)
-            ids = torch.tensor(flat, dtype=torch.int64, device=self._device)
+            batch = nsq.Batch(slots, pos0, [1] * B, self._device, parity)
+            both = torch.tensor(flat + prev, dtype=torch.int64, device=self._device)
+            ids, batch.prev_ids = both[:B], both[B:]
             rows_t = torch.arange(B, dtype=torch.int32, device=self._device)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -107,13 +115,13 @@ class SlotPoolCausalLM(nn.Module):
             with torch.cuda.graph(graph):  # recording only: no kernel runs, no state advances
                 out = self._layers(ids, batch, rows_t)
             # every tensor the recorded kernels read must outlive the graph: the row list too
-            entry = (graph, batch, ids, out, nsq.launch_count() - before, rows_t)
+            entry = (graph, batch, both, out, nsq.launch_count() - before, rows_t)
             self._graphs[key] = entry
-        graph, batch, ids, out, n_native = entry[:5]
+        graph, batch, both, out, n_native = entry[:5]
         ar = list(range(B))
-        host = torch.tensor(ar + list(pos0) + list(slots) + list(pos0) + [1] * B + ar, dtype=torch.int32)
+        host = torch.tensor(ar + list(pos0) + list(slots) + list(pos0) + [1] * B + ar + list(parity), dtype=torch.int32)
         batch.meta.copy_(host.pin_memory(), non_blocking=True)
-        ids.copy_(torch.tensor(flat, dtype=torch.int64).pin_memory(), non_blocking=True)
+        both.copy_(torch.tensor(flat + prev, dtype=torch.int64).pin_memory(), non_blocking=True)
         graph.replay()
         nsq.note_replayed_launches(n_native)
         return out.clone()

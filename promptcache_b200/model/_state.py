@@ -7,6 +7,9 @@ layer has pool tensors whose first dimension is the slot,
 
     attention layer   K [slots, Hkv, cap, dim]   V [slots, Hkv, cap, vdim]        (compute type)
     matrix memory     S [slots, H, dim, vdim]    n [slots, H, dim]    m [slots, H]  (float32)
+    short convolution tail [slots, 2, taps - 1, width]                             (float32, double-buffered)
+
+(a layer's spec may be a tuple of these, or None for a layer that reads another layer's rows)
 
 so that one kernel launch serves a whole batch: it gets the slot of every batch entry and the number of tokens the slot
 already holds.  A slot that is released is handed out again; nothing is cleared, because every consumer starts a sequence
@@ -38,6 +41,14 @@ class MatrixMemorySpec:
     vdim: int
 
 
+@dataclass(frozen=True)
+class ConvTailSpec:
+    """The last `taps - 1` inputs of a causal convolution over time on `width` channels, kept twice: a step reads one copy
+    and writes the other (the sequence's step parity says which), so that one launch can do both for a whole batch."""
+    taps: int
+    width: int
+
+
 class SlotPool:
     def __init__(self, specs: List[object], dtype: torch.dtype, device, n_slots: int = 2, cap: int = 128,
                  max_tokens: Optional[int] = None):
@@ -56,6 +67,15 @@ class SlotPool:
         return cap
 
     def _alloc(self, spec, n_slots: int, cap: int) -> Dict[str, torch.Tensor]:
+        if spec is None:  # a layer that keeps nothing (it reads another layer's rows)
+            return {}
+        if isinstance(spec, (tuple, list)):  # a layer with several kinds of state
+            out: Dict[str, torch.Tensor] = {}
+            for part in spec:
+                out.update(self._alloc(part, n_slots, cap))
+            return out
+        if isinstance(spec, ConvTailSpec):
+            return {"tail": torch.zeros(n_slots, 2, max(spec.taps - 1, 1), spec.width, dtype=torch.float32, device=self.device)}
         if isinstance(spec, KVSpec):
             return {"k": torch.zeros(n_slots, spec.n_kv_heads, cap, spec.dim, dtype=self.dtype, device=self.device),
                     "v": torch.zeros(n_slots, spec.n_kv_heads, cap, spec.vdim, dtype=self.dtype, device=self.device)}
@@ -112,6 +132,8 @@ class SeqState:
 
     def __init__(self, pool: SlotPool):
         self.pool, self.slot = pool, pool.acquire()
+        self.steps = 0           # steps this sequence has run (its parity selects the copy of double-buffered state)
+        self.last_token = -1     # the sequence's latest token id (designs whose embedding looks at the previous token)
 
     @property
     def rows(self) -> int:
