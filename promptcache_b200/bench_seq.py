@@ -1,5 +1,6 @@
-"""Throughput of the slot-pool design (Mutolix) beside the closest prompt-cache model (Llama) at equal sizes: `bench.py
---design mutolix`.  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
+"""Throughput of the slot-pool designs beside the closest existing model at equal sizes: `bench.py --design mutolix`
+(against the Llama prompt-cache path) and `bench.py --design raritar` (against Mutolix's attention layers with a dense
+feed-forward of the same active size, which share the step function, the pool and the attention kernels).  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
 step / forward, then every kernel of the new design alone against its roofline, next to the like kernel of the Llama path.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up iterations, a 256 MiB write between timed iterations (flushes the
@@ -204,7 +205,182 @@ def kernel_block(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: flo
     return out
 
 
+# ---- Raritar ----------------------------------------------------------------------------------------------------------
+RARITAR_SIZES = {
+    # width, heads / kv heads / dim / vdim, window, experts / pass-through / top / groups / expert ff / shared ff, layers, vocab
+    "w1024": dict(width=1024, H=8, G=2, D=128, V=128, window=512, keep=4, E=8, I=2, top=2, groups=(2, 1), ff=1024, sff=2048, layers=4, vocab=8192),
+    "w2048": dict(width=2048, H=16, G=4, D=128, V=128, window=1024, keep=4, E=16, I=0, top=4, groups=(4, 2), ff=1024, sff=4096, layers=8, vocab=8192),
+}
+
+
+def raritar_config(s: dict) -> dict:
+    def layer(kv_from=None):
+        mixer = {"heads": s["H"], "kv_heads": s["G"], "dim": s["D"], "vdim": s["V"], "scale": s["D"] ** -0.5, "softcap": 50.0,
+                 "mask": {"size": s["window"], "keep_first": s["keep"]},
+                 "rot": {"base": 10000.0, "dims": s["D"] // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+        if kv_from is not None:
+            mixer["kv_from"] = kv_from
+        mlp = {"kind": "moe", "expert": {"ff": s["ff"]}, "shared": {"ff": s["sff"]},
+               "router": {"experts": s["E"], "identity": s["I"], "top": s["top"], "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
+        return {"type": "attention", "mixer": mixer, "mlp": mlp}
+    own = s["layers"] - s["layers"] // 4       # the last quarter of the layers reads the rows of the last layer that has its own
+    return {"architecture": "Raritar", "vocab": s["vocab"], "width": s["width"], "residual_mult": 0.7, "norm": {"eps": 1e-5},
+            "canon": {"taps": 4}, "embedding": {"bigram": {"buckets": 4093, "mul_prev": 31, "mul_cur": 7}},
+            "layers": [layer() for _ in range(own)] + [layer(own - 1) for _ in range(s["layers"] - own)]}
+
+
+def raritar_tensors(cfg: dict, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    W, t = cfg["width"], {}
+    rnd = lambda *shape, std=1.0, mean=0.0: (torch.randn(*shape, generator=g, device=device) * std + mean).to(torch.bfloat16)
+    lin = lambda o, i: rnd(o, i, std=i ** -0.5)
+    t["embed"], t["final.norm"], t["head"] = rnd(cfg["vocab"], W), rnd(1, std=0.05, mean=1.0).reshape(()), lin(cfg["vocab"], W)
+    t["bigram"] = rnd(cfg["embedding"]["bigram"]["buckets"] + 1, W, std=0.5)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, f = f"l{i}.", layer["mixer"], layer["mlp"]
+        t[p + "norm1"], t[p + "norm2"] = rnd(1, std=0.05, mean=1.0).reshape(()), rnd(1, std=0.05, mean=1.0).reshape(())
+        t[p + "canon1"] = rnd(W, cfg["canon"]["taps"], std=0.3)
+        H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        t[p + "mix.q"], t[p + "mix.o"] = lin(H * D, W), lin(W, H * V)
+        if "kv_from" not in m:
+            t[p + "mix.k"], t[p + "mix.v"] = lin(G * D, W), lin(G * V, W)
+        r = f["router"]
+        t[p + "mlp.router"], t[p + "mlp.correction"] = rnd(r["experts"] + r["identity"], W, std=3 * W ** -0.5), rnd(r["experts"] + r["identity"], std=0.05)
+        for name, ff in [(f"e{e}.", f["expert"]["ff"]) for e in range(r["experts"])] + [("shared.", f["shared"]["ff"])]:
+            t[p + "mlp." + name + "gate"], t[p + "mlp." + name + "up"], t[p + "mlp." + name + "down"] = lin(ff, W), lin(ff, W), lin(W, ff)
+        t[p + "mlp.shared.sg"] = lin(1, W)
+    return t
+
+
+def _throughput(m, s: dict, timer: Timer, prompt: int, batch: int, ctx: int, out: dict, prefix: str = "") -> None:
+    """Prefill of one prompt and of `batch` prompts, decode of 1 and of `batch` sequences at `ctx` tokens, through step()."""
+    g = torch.Generator().manual_seed(1)
+    toks = lambda n: torch.randint(0, s["vocab"], (n,), generator=g).tolist()
+    seqs: List = []
+
+    def fresh(n):
+        for q in seqs:
+            q.free()
+        seqs[:] = [m.new_sequence() for _ in range(n)]
+
+    p1, pb = toks(prompt), [toks(prompt // 2) for _ in range(batch)]
+    ms = timer(lambda: m.step([(seqs[0], p1)]), setup=lambda: fresh(1), steps=5)
+    out[prefix + "prefill_1x%d_tok_s" % prompt] = round(prompt / ms * 1e3)
+    ms = timer(lambda: m.step([(q, t) for q, t in zip(seqs, pb)]), setup=lambda: fresh(batch), steps=5)
+    out[prefix + "prefill_%dx%d_tok_s" % (batch, prompt // 2)] = round(batch * (prompt // 2) / ms * 1e3)
+    for nb in (1, batch):
+        fresh(nb)
+        m.step([(q, toks(ctx)) for q in seqs])
+        for _ in range(3):  # the second one-token step of a batch size captures its graph
+            m.step([(q, [1]) for q in seqs])
+        ms = timer(lambda: m.step([(q, [1]) for q in seqs]), steps=16)
+        out[prefix + "decode_b%d_ms_per_step" % nb] = round(ms, 4)
+    fresh(0)
+
+
+def raritar_block(s: dict, dev, timer: Timer, prompt: int, batch: int, ctx: int) -> dict:
+    from .model.mutolix import MutolixConfig, MutolixForCausalLM
+    from .model.raritar import RaritarConfig, RaritarForCausalLM
+    cfg = raritar_config(s)
+    out = {"layers": len(cfg["layers"]), "width": s["width"], "active_ff": s["top"] * s["ff"] + s["sff"]}
+    m = RaritarForCausalLM(RaritarConfig(cfg), raritar_tensors(cfg, dev), device=dev, dtype=torch.bfloat16)
+    _throughput(m, s, timer, prompt, batch, ctx, out)
+    del m
+    torch.cuda.empty_cache()
+    # the closest existing model: Mutolix's attention layers (full causal attention, every layer with rows of its own) with a
+    # dense feed-forward as wide as this design's active experts
+    attn = {"type": "attention", "mixer": {"heads": s["H"], "kv_heads": s["G"], "dim": s["D"], "vdim": s["V"], "scale": s["D"] ** -0.5},
+            "mlp": {"kind": "dense", "ff": out["active_ff"]}}
+    mc = {"architecture": "Mutolix", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+          "layers": [attn] * s["layers"]}
+    mm = MutolixForCausalLM(MutolixConfig(mc), random_tensors(mc, dev), device=dev, dtype=torch.bfloat16)
+    _throughput(mm, s, timer, prompt, batch, ctx, out, prefix="mutolix_")
+    del mm
+    torch.cuda.empty_cache()
+    return out
+
+
+def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: float, tflops: float) -> dict:
+    """Every kernel of the design alone at this size, achieved / peak, beside the like kernel of the closest model."""
+    from . import _native_seq as nsq
+    bf, H, G, D, V, W = torch.bfloat16, s["H"], s["G"], s["D"], s["V"], s["width"]
+    win, keep, E, top, ff = s["window"], s["keep"], s["E"], s["top"], s["ff"]
+    out = {}
+    gb = lambda by, ms: {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    tf = lambda fl, ms: {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_measured_bf16_peak": round(fl / ms / 1e9 / tflops, 3)}
+    cap = ((max(prompt, ctx + 1) + 127) // 128) * 128
+    kp, vp = torch.randn(1, G, cap, D, device=dev).to(bf), torch.randn(1, G, cap, V, device=dev).to(bf)
+    b = nsq.Batch([0], [0], [prompt], dev)
+    q, o = torch.randn(prompt, H * D, device=dev).to(bf), torch.empty(prompt, H * V, device=dev, dtype=bf)
+    # prompt attention: FLOPs = 2 (D + V) per (query, VISIBLE key) pair and head
+    pairs = sum(min(i + 1, win) + max(0, min(keep, i + 1 - win)) for i in range(prompt))
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, softcap=50.0, window=win, keep_first=keep))
+    out["attn_prompt_window"] = tf(2.0 * (D + V) * H * pairs, ms)
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, softcap=50.0))
+    out["attn_prompt_capped_full"] = tf(2.0 * (D + V) * H * prompt * (prompt + 1) / 2, ms)
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b))
+    out["like_attn_prompt_full"] = tf(2.0 * (D + V) * H * prompt * (prompt + 1) / 2, ms)
+    # one decoded token: bytes = visible K and V rows of every kv head
+    b1 = nsq.Batch([0], [ctx], [1], dev)
+    q1, o1 = torch.randn(1, H * D, device=dev).to(bf), torch.empty(1, H * V, device=dev, dtype=bf)
+    wsd = nsq.attn_workspace(1, H, V, dev)
+    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, None, None, False, b1, max_keys=win + keep, workspace=wsd, softcap=50.0, window=win,
+                                     keep_first=keep), steps=15)
+    out["attn_decode_window"] = gb(2.0 * G * (win + keep) * (D + V), ms)
+    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, None, None, False, b1, max_keys=cap, workspace=wsd), steps=15)
+    out["like_attn_decode_full"] = gb(2.0 * G * (ctx + 1) * (D + V), ms)
+    # norm + convolution: reads x (4 B, neighbours from L2) and writes h (2 B); like: gated norm + residual + next norm
+    x, h = torch.randn(prompt, W, device=dev), torch.empty(prompt, W, device=dev, dtype=bf)
+    g1, cw, tail = torch.ones(1, device=dev, dtype=bf), (torch.randn(W, 4, device=dev) * 0.3).to(bf), torch.zeros(1, 2, 3, W, device=dev)
+    ms = timer(lambda: nsq.norm_conv(x, g1, 1e-5, h, conv_w=cw, tail=tail, batch=b))
+    out["norm_conv"] = gb(prompt * W * 6.0, ms)
+    y = torch.randn(prompt, W, device=dev).to(bf)
+    ms = timer(lambda: nsq.norm_conv(x, g1, 1e-5, h, y=y, y_mult=0.7))
+    out["add_norm"] = gb(prompt * W * 12.0, ms)
+    wn = torch.ones(W, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.gate_norm_add(x, y, None, wn, None, 1e-5, wn, h))
+    out["like_gate_norm_add"] = gb(prompt * W * 12.0, ms)
+    # rotation + value norm + append: reads the projection row, writes q, k, v (2 B each); like: Mutolix's q/k norm + append
+    nq, nk = H * D, G * (D + V)
+    proj = torch.randn(prompt, nq + nk, device=dev).to(bf)
+    fr = torch.tensor([10000.0 ** (-2.0 * i / (D // 2)) for i in range(D // 4)], dtype=torch.float64, device=dev)
+    ms = timer(lambda: nsq.rope_kv_prep(proj, (0, nq, nq + G * D), H, G, D, V, fr, D // 2, True, True, 1e-5, q, kp, vp, b))
+    out["rope_kv_prep"] = gb(prompt * (nq + nk) * 4.0, ms)
+    qn, kn = torch.ones(nq, device=dev, dtype=bf), torch.ones(G * D, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.qk_prep(proj, (0, nq, nq + G * D), qn, kn, 1e-5, H, G, D, V, 0.0, 0, q, kp, vp, None, None, b))
+    out["like_qk_prep"] = gb(prompt * (nq + nk) * 4.0, ms)
+    # router
+    hb = torch.randn(prompt, W, device=dev).to(bf)
+    wr, corr, wsg = (torch.randn(E + s["I"], W, device=dev) * 3 * W ** -0.5).to(bf), torch.zeros(E + s["I"], device=dev), torch.randn(W, device=dev).to(bf)
+    ms = timer(lambda: nsq.moe_route(hb, wr, corr, wsg, top, s["groups"][0], s["groups"][1]))
+    out["moe_route"] = gb(prompt * W * 2.0, ms)
+    idx, _, _ = nsq.moe_route(hb, wr, corr, wsg, top, s["groups"][0], s["groups"][1])
+    real = int((idx < E).sum())
+    # the experts of a prompt: FLOPs = 6 ff W per real pair; like: the dense feed-forward's library products of the same FLOPs
+    wgu, wdn = (torch.randn(E, 2 * ff, W, device=dev) * W ** -0.5).to(bf), (torch.randn(E, W, ff, device=dev) * ff ** -0.5).to(bf)
+    ms = timer(lambda: nsq.moe_experts(hb, idx, wgu, wdn, grouped=True))
+    out["moe_experts_prompt"] = dict(tf(6.0 * ff * W * real, ms), pairs=real)
+    rows = max(real, 1)
+    xa, wa, wb2 = torch.randn(rows, W, device=dev).to(bf), wgu[0], wdn[0]
+    ms = timer(lambda: torch.nn.functional.linear(torch.nn.functional.linear(xa, wa)[:, :ff], wb2))
+    out["like_dense_ff_products"] = tf(6.0 * ff * W * rows, ms)
+    # the experts of one decoded token: bytes = the chosen experts' three matrices; like: the few-row linear kernel on as many bytes
+    i1 = idx[:1].contiguous()
+    real1 = int((i1 < E).sum())
+    ms = timer(lambda: nsq.moe_experts(hb[:1], i1, wgu, wdn, grouped=False), steps=15)
+    out["moe_experts_decode"] = gb(real1 * 3.0 * ff * W * 2, ms)
+    wl = (torch.randn(real1 * 3 * ff, W, device=dev) * W ** -0.5).to(bf)
+    ms = timer(lambda: nsq.linear(hb[:1], wl, kernel=True), steps=15)
+    out["like_linear_rows"] = gb(real1 * 3.0 * ff * W * 2, ms)
+    ye, wg2, sg, ys = torch.randn(prompt * top, W, device=dev), torch.rand(prompt, top, device=dev), torch.rand(prompt, device=dev), torch.randn(prompt, W, device=dev).to(bf)
+    ms = timer(lambda: nsq.moe_combine(x, ye, idx, wg2, hb, E, 0.7, ys=ys, shared_gate=sg))
+    out["moe_combine"] = gb(prompt * W * (4.0 * top + 2 + 8), ms)
+    return out
+
+
 def run(args, load_peaks, ClockSampler) -> None:
+    if args.design == "raritar":
+        return run_raritar(args, load_peaks, ClockSampler)
     from . import _native as nat, _native_seq as nsq, build as pc_build
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -226,5 +402,30 @@ def run(args, load_peaks, ClockSampler) -> None:
         blk["kernels"] = kernel_block(s, dev, timer, prompt, ctx, hbm, tfl)
         line["sizes"][name] = blk
     line["gpu_launches"] = nat.launch_count() + nsq.launch_count() - before
+    line["clocks"] = sampler.stop()
+    print(json.dumps(line), flush=True)
+
+
+def run_raritar(args, load_peaks, ClockSampler) -> None:
+    from . import _native_seq as nsq
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nsq.load()
+    hbm, kind, tfl = load_peaks()
+    timer = Timer(dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark()
+    before = nsq.launch_count()
+    line = {"design": "raritar", "compared_with": "mutolix attention layers (full causal attention, dense feed-forward of the active size) on the same "
+                                                  "step function, pool and kernels",
+            "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "kind": kind},
+            "timing": "CUDA events, 3 warm-up iterations, 256 MiB L2 flush between iterations, median", "sizes": {}}
+    prompt, batch, ctx = 2048, 4, 2048
+    for name, s in RARITAR_SIZES.items():
+        blk = raritar_block(s, dev, timer, prompt, batch, ctx)
+        blk["kernels"] = raritar_kernels(s, dev, timer, prompt, ctx, hbm, tfl)
+        line["sizes"][name] = blk
+    line["gpu_launches"] = nsq.launch_count() - before
     line["clocks"] = sampler.stop()
     print(json.dumps(line), flush=True)

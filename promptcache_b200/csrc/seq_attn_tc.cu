@@ -5,6 +5,8 @@
 // while the current one is multiplied; V in one, loaded during the score phase), fragments come from ldmatrix, products are
 // m16n8k16 bfloat16 tensor-core operations with 32-bit accumulators held in registers:
 //     S = Q K^T           32-bit scores; scale, distance bias r1 ln(1 + r2 (i - j)) and the causal mask applied per score
+//                         (a cap cap * tanh(s / cap) before the bias; a sliding window with kept first keys: key tiles that
+//                         no row of the block sees are skipped)
 //     online softmax      running maximum / sum per query row in 32-bit; a sink starts them at (0, 1) instead of (-inf, 0)
 //     O += P V            the 32-bit weights enter the tensor cores as TWO bfloat16 operands, P = hi + lo with
 //                         hi = bf16(P), lo = bf16(P - hi), so that the product keeps ~16 bits of every weight instead of 8
@@ -97,16 +99,31 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
                           ((warp * 16 + (lane & 15)) * (DP + PAD) + (lane >> 4) * 8) * 2;
   const uint32_t k_base0 = static_cast<uint32_t>(__cvta_generic_to_shared(Kbuf)) + (((lane & 7)) * (DP + PAD) + (lane >> 3) * 8) * 2;
   const uint32_t v_base0 = static_cast<uint32_t>(__cvta_generic_to_shared(Vbuf)) + ((lane & 15) * (VP + PAD) + (lane >> 4) * 8) * 2;
-  load_tile_async<DP>(Kbuf, Kg, D, 0, total_keys, D);
+  // With a window the key tiles a block walks are the tiles of the kept first keys and then the tiles from the one that holds
+  // the lowest key its first row sees; when the two parts touch, all tiles from 0.  Tile `it` of the walk starts at key
+  // (it < n_first ? it : lo_tile + it - n_first) * 64.
+  const bool windowed = p.window > 0;
+  int lo_tile = 0, n_first = 0;
+  if (windowed) {
+    lo_tile = max(0, pos0 + q0 - p.window + 1) / BN;
+    n_first = (min(max(p.keep_first, 0), total_keys) + BN - 1) / BN;
+    if (n_first >= lo_tile) { n_first = 0; lo_tile = 0; }
+  }
+  const int n_it = n_first + (n_keys + BN - 1) / BN - lo_tile;
+  const float cap_in = p.softcap > 0.f ? p.scale / p.softcap * 2.885390081777927f : 0.f;  // 2 log2(e) scale / cap
+  const float cap_out = p.softcap * 1.4426950408889634f;
+  load_tile_async<DP>(Kbuf, Kg, D, (n_first > 0 ? 0 : lo_tile) * BN, total_keys, D);
   cp_async_commit();
 
   // K in two stages, V in one (three blocks of 4 warps fit an SM at widths up to 128): per tile the copies are committed in
   // the order V_t, K_{t+1}; K_t is complete when at most those two groups are pending, V_t when at most one is
-  for (int k0 = 0, it = 0; k0 < n_keys; k0 += BN, ++it) {
+  for (int it = 0; it < n_it; ++it) {
     const int st = it & 1;
+    const int k0 = (it < n_first ? it : lo_tile + it - n_first) * BN;
     load_tile_async<VP>(Vbuf, Vg, V, k0, total_keys, V);  // has the score phase to arrive
     cp_async_commit();
-    if (k0 + BN < n_keys) load_tile_async<DP>(Kbuf + (st ^ 1) * BN * (DP + PAD), Kg, D, k0 + BN, total_keys, D);
+    if (it + 1 < n_it)
+      load_tile_async<DP>(Kbuf + (st ^ 1) * BN * (DP + PAD), Kg, D, (it + 1 < n_first ? it + 1 : lo_tile + it + 1 - n_first) * BN, total_keys, D);
     cp_async_commit();  // (an empty group after the last tile keeps the counts the same)
     if (bias) {  // this tile's distance biases, one per thread: entry y belongs to distance (q0 - k0) + 63 - y
       const int y = threadIdx.x, d = pos0 + q0 - k0 + 63 - y;
@@ -138,7 +155,8 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
     }
     // ---- scores in the base-2 domain: s * scale * log2(e) - bias (from the tile's table); causal mask only where a tile
     //      reaches past the warp's first row or the last key; row maxima ----
-    const bool need_mask = (k0 + BN - 1 > pos0 + q0 + warp * 16) || (k0 + BN > total_keys);
+    const bool need_mask = (k0 + BN - 1 > pos0 + q0 + warp * 16) || (k0 + BN > total_keys) ||
+                           (windowed && pos0 + q0 + warp * 16 + 15 - k0 >= p.window);
     float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
@@ -147,16 +165,28 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
         ba = *reinterpret_cast<const float2*>(tp_a + nt * 8);
         bb = *reinterpret_cast<const float2*>(tp_a + nt * 8 - 8);
       }
-      s[nt][0] = fmaf(s[nt][0], scale2, -ba.x);
-      s[nt][1] = fmaf(s[nt][1], scale2, -ba.y);
-      s[nt][2] = fmaf(s[nt][2], scale2, -bb.x);
-      s[nt][3] = fmaf(s[nt][3], scale2, -bb.y);
+      if (p.softcap > 0.f) {  // cap tanh(s scale / cap) as 1 - 2 / (1 + e^(2x)), then to the base-2 domain
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[nt][c] = (1.f - __fdividef(2.f, 1.f + ex2(s[nt][c] * cap_in))) * cap_out;
+        s[nt][0] -= ba.x; s[nt][1] -= ba.y; s[nt][2] -= bb.x; s[nt][3] -= bb.y;
+      } else {
+        s[nt][0] = fmaf(s[nt][0], scale2, -ba.x);
+        s[nt][1] = fmaf(s[nt][1], scale2, -ba.y);
+        s[nt][2] = fmaf(s[nt][2], scale2, -bb.x);
+        s[nt][3] = fmaf(s[nt][3], scale2, -bb.y);
+      }
       if (need_mask) {
         const int pk = k0 + nt * 8 + qd * 2;
         if (pk > pq_a || pk >= total_keys) s[nt][0] = -INFINITY;
         if (pk + 1 > pq_a || pk + 1 >= total_keys) s[nt][1] = -INFINITY;
         if (pk > pq_b || pk >= total_keys) s[nt][2] = -INFINITY;
         if (pk + 1 > pq_b || pk + 1 >= total_keys) s[nt][3] = -INFINITY;
+        if (windowed) {
+          if (pq_a - pk >= p.window && pk >= p.keep_first) s[nt][0] = -INFINITY;
+          if (pq_a - pk - 1 >= p.window && pk + 1 >= p.keep_first) s[nt][1] = -INFINITY;
+          if (pq_b - pk >= p.window && pk >= p.keep_first) s[nt][2] = -INFINITY;
+          if (pq_b - pk - 1 >= p.window && pk + 1 >= p.keep_first) s[nt][3] = -INFINITY;
+        }
       }
       mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
       mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
@@ -165,18 +195,20 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    // key 0 is visible to every row, so the maxima are finite from the first tile on; a masked score gives 2^-inf = 0
+    // a masked score gives 2^-inf = 0; a row that has seen no key yet (under a window the first tile of the walk may hold
+    // none of a later row's keys) keeps its maximum at minus infinity and subtracts 0 instead
     const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
     const float f_a = (m_a == -INFINITY) ? 0.f : ex2(m_a - mn_a), f_b = (m_b == -INFINITY) ? 0.f : ex2(m_b - mn_b);
     m_a = mn_a;
     m_b = mn_b;
+    const float sub_a = mn_a == -INFINITY ? 0.f : mn_a, sub_b = mn_b == -INFINITY ? 0.f : mn_b;
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
-      s[nt][0] = ex2(s[nt][0] - mn_a);
-      s[nt][1] = ex2(s[nt][1] - mn_a);
-      s[nt][2] = ex2(s[nt][2] - mn_b);
-      s[nt][3] = ex2(s[nt][3] - mn_b);
+      s[nt][0] = ex2(s[nt][0] - sub_a);
+      s[nt][1] = ex2(s[nt][1] - sub_a);
+      s[nt][2] = ex2(s[nt][2] - sub_b);
+      s[nt][3] = ex2(s[nt][3] - sub_b);
       sum_a += s[nt][0] + s[nt][1];
       sum_b += s[nt][2] + s[nt][3];
     }
@@ -262,7 +294,6 @@ int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled) {
   *handled = false;
   if (p.dtype != PCS_BF16 || p.max_len < 16 || p.dim % 8 != 0 || p.vdim % 8 != 0 || p.dim > 256 || p.vdim > 256) return PCS_OK;
   if (!p.seq_pos0 || !p.seq_len || !p.seq_off) return PCS_OK;
-  if (p.window > 0 || p.softcap > 0.f) return PCS_OK;
   if (static_cast<long long>((p.max_len + BM - 1) / BM) * p.n_seqs * p.n_heads > 0x7fffffffLL) return PCS_OK;
   *handled = true;
   if (p.dim <= 64) return launch_v<64>(p, st);

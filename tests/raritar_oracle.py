@@ -216,3 +216,30 @@ def random_model(cfg, seed=0, scale=0.5):
             if f.get("shared"):
                 W[p + "mlp.shared.sg"] = mat(1, Wd, 2.0 / math.sqrt(Wd))
     return W
+
+
+def attn_layer(heads=4, kv_heads=2, dim=16, vdim=8, window=12, keep_first=3, rot_dims=8, scaling=True, softcap=30.0, kv_from=None,
+               experts=6, identity=2, top=3, groups=(4, 2), ff=24, shared_ff=16, mlp=True):
+    """One layer's configuration entry (small sizes; every key the design reads)."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window, "keep_first": keep_first},
+             "rot": {"base": 10000.0, "dims": rot_dims}, "scale": 1.3 / math.sqrt(dim), "softcap": softcap}
+    if scaling:
+        mixer["rot"]["scaling"] = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    f = None
+    if mlp:
+        f = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": identity, "top": top,
+                                                            "groups": {"count": groups[0], "keep": groups[1]}}}
+        if shared_ff:
+            f["shared"] = {"ff": shared_ff}
+    return {"type": "attention", "mixer": mixer, "mlp": f}
+
+
+def make_config(layers, width=40, vocab=61, taps=4, buckets=53, mult=0.6, eps=1e-5):
+    cfg = {"architecture": "Raritar", "vocab": vocab, "width": width, "residual_mult": mult, "norm": {"eps": eps}, "layers": layers}
+    if taps:
+        cfg["canon"] = {"taps": taps}
+    if buckets:
+        cfg["embedding"] = {"bigram": {"buckets": buckets, "mul_prev": 29, "mul_cur": 5}}
+    return cfg
