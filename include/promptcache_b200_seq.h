@@ -181,7 +181,7 @@ int pcs_embed_bigram(const void* table, const void* pair, const int64_t* ids, co
                      int width, int vocab, int64_t buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream);
 
 /* Per token t:  x[t] += y_mult * y[t]  (y may be NULL),  u[t] = x[t] / sqrt(mean(x[t]^2) + eps) * g,
- *               h_out[t] = u[t] + sum_{j < taps} conv_w[:, j] * u[t - taps + 1 + j]        (conv_w NULL: h_out = u)
+ *               h_out[t] = u[t] + sum_{j < taps} conv_w[j, :] * u[t - taps + 1 + j]        (conv_w NULL: h_out = u)
  * u of tokens before the sequence's start is zero; u of tokens of earlier steps comes from `tail`, which holds the last
  * taps - 1 inputs of every slot twice: a step reads copy seq_par[b] and writes copy 1 - seq_par[b] (the caller alternates
  * seq_par from step to step), so no block reads what another one writes.  y and conv_w together are not supported (the
@@ -194,7 +194,7 @@ typedef struct pcs_normconv_params {
   const void* g;            /* `dtype`: g_len == 1 one number for all channels, else [width] */
   int32_t g_len;
   float eps;
-  const void* conv_w;       /* [width, taps] `dtype`, or NULL */
+  const void* conv_w;       /* [taps, width] `dtype` (tap-major: a tap's weights of neighbouring channels are one load), or NULL */
   int32_t taps;
   float* tail;              /* [slots, 2, taps - 1, width] fp32 */
   void* h_out;              /* [n_tokens, width] `dtype`, or NULL */
@@ -257,19 +257,26 @@ int pcs_moe_rows_down(const void* act, const void* w_down, const int32_t* idx, f
                       int dtype, void* stream);
 
 /* Many rows: pairs are sorted by expert on the device.  `plan` is int32 scratch of pcs_moe_plan_ints(n_pairs, n_experts)
- * elements: [0] number of row tiles, then per tile (expert, first sorted row, rows), then the sorted pair list. */
+ * elements; pcs_moe_plan_part(part, ...) gives the offset of part 0: the experts' cumulative row ends [n_experts] (16-byte
+ * aligned), 1: per row tile (expert, first sorted row, rows), 2: the sorted pair list [n_pairs], 3: every pair's sorted row
+ * [n_pairs] (-1 for a pass-through choice).  plan[0] is the number of row tiles. */
 int64_t pcs_moe_plan_ints(int n_pairs, int n_experts);
+int pcs_moe_plan_part(int part, int n_pairs, int n_experts);
 int pcs_moe_plan(const int32_t* idx, int n_pairs, int n_experts, int32_t* plan, void* stream);
+/* out[r, :] = h[sorted pair r / top, :] for the rows in use (bfloat16, width a multiple of 8): the left operand of a grouped product */
+int pcs_moe_gather(const void* h, int64_t h_stride, const int32_t* plan, void* out, int n_pairs, int top, int n_experts, int width,
+                   void* stream);
 /* stage 0: act[sorted row, :] = silu(W_gate_e h[pair / top]) * (W_up_e h[pair / top])   (bf16 [n_pairs, ff])
  * stage 1: y[pair, :] = W_down_e act[sorted row, :]                                      (fp32 [n_pairs, width])
  * bfloat16 only; ff and width multiples of 8. */
 int pcs_moe_gemm(int stage, const void* a, int64_t a_stride, const void* w, const int32_t* plan, void* out, int n_pairs, int top,
                  int n_experts, int ff, int width, void* stream);
 
-/* x[t] += mult * ( sum_k wgt[t,k] * (idx[t,k] < n_experts ? y[t*top + k] : h[t]) + (ys ? shared_gate[t] * ys[t] : 0) ) */
+/* x[t] += mult * ( sum_k wgt[t,k] * (idx[t,k] < n_experts ? y[row(t*top + k)] : h[t]) + (ys ? shared_gate[t] * ys[t] : 0) )
+ * row(p) = y_row ? y_row[p] : p;  y is fp32 (y_dtype PCS_F32) or `dtype`. */
 typedef struct pcs_combine_params {
   float* x;                 /* [n_tokens, width] */
-  const float* y;           /* [n_tokens * top, width] */
+  const void* y;            /* [rows, width] */
   const int32_t* idx;
   const float* wgt;
   const void* h;            /* [n_tokens, h_stride] `dtype`: what pass-through outputs hand on */
@@ -278,7 +285,8 @@ typedef struct pcs_combine_params {
   int64_t ys_stride;
   const float* shared_gate; /* [n_tokens] or NULL (ys is added as it is) */
   float mult;
-  int32_t n_tokens, width, top, n_experts, dtype, reserved;
+  int32_t n_tokens, width, top, n_experts, dtype, y_dtype;
+  const int32_t* y_row;     /* [n_tokens * top] or NULL */
 } pcs_combine_params;
 int pcs_moe_combine(const pcs_combine_params* p, void* stream);
 

@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(_HERE, "libpromptcache_b200_seq.so")
 PCS_BF16, PCS_F32 = 0, 1
 EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_attn_workspace_floats", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu", "pcs_linear_rows",
            "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan", "pcs_embed_bigram", "pcs_norm_conv", "pcs_rope_kv_prep", "pcs_moe_route",
-           "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul")
+           "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gather", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul")
 
 
 class pcs_gna_params(C.Structure):
@@ -75,7 +75,7 @@ class pcs_combine_params(C.Structure):
     _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("h", C.c_void_p), ("h_stride", C.c_int64),
                 ("ys", C.c_void_p), ("ys_stride", C.c_int64), ("shared_gate", C.c_void_p), ("mult", C.c_float),
                 ("n_tokens", C.c_int32), ("width", C.c_int32), ("top", C.c_int32), ("n_experts", C.c_int32), ("dtype", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("y_dtype", C.c_int32), ("y_row", C.c_void_p)]
 
 
 class pcs_mlstm_params(C.Structure):
@@ -132,6 +132,9 @@ def load() -> C.CDLL:
     lib.pcs_moe_plan_ints.argtypes = [C.c_int, C.c_int]
     lib.pcs_moe_plan_ints.restype = C.c_int64
     lib.pcs_moe_plan.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.pcs_moe_plan_part.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.pcs_moe_plan_part.restype = C.c_int
+    lib.pcs_moe_gather.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pcs_moe_gemm.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                  C.c_void_p]
     lib.pcs_moe_combine.argtypes = [C.POINTER(pcs_combine_params), C.c_void_p]
@@ -387,8 +390,9 @@ def embed_bigram(table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, pre
 
 def norm_conv(x: torch.Tensor, g: Optional[torch.Tensor], eps: float, h_out: Optional[torch.Tensor], y: Optional[torch.Tensor] = None,
               y_mult: float = 1.0, conv_w: Optional[torch.Tensor] = None, tail: Optional[torch.Tensor] = None, batch: Optional[Batch] = None) -> None:
-    """x += y_mult * y (when y is given); h_out = u + causal_conv(u) with u = rms_norm(x) * g (g: one number or [width]).  `tail`
-    [slots, 2, taps - 1, width] float32 carries the last inputs of every slot from step to step."""
+    """x += y_mult * y (when y is given); h_out = u + causal_conv(u) with u = rms_norm(x) * g (g: one number or [width]).  conv_w is
+    [taps, width], the last tap weighing the token itself.  `tail` [slots, 2, taps - 1, width] float32 carries the last inputs
+    of every slot from step to step."""
     _cuda(x, g, h_out, y, conv_w, tail)
     if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
         raise NativeError("norm_conv: x must be a contiguous float32 matrix")
@@ -405,9 +409,9 @@ def norm_conv(x: torch.Tensor, g: Optional[torch.Tensor], eps: float, h_out: Opt
             raise NativeError("norm_conv: g is one number or [width] in h_out's type; h_out contiguous of x's shape")
         p.g, p.g_len, p.h_out = g.data_ptr(), g.numel(), h_out.data_ptr()
     if conv_w is not None:
-        taps = conv_w.shape[1]
-        if conv_w.dtype != dt or not conv_w.is_contiguous() or conv_w.shape[0] != x.shape[1] or batch is None:
-            raise NativeError("norm_conv: conv_w must be contiguous [width, taps] in the compute type, with the batch given")
+        taps = conv_w.shape[0]
+        if conv_w.dtype != dt or not conv_w.is_contiguous() or conv_w.shape[1] != x.shape[1] or batch is None:
+            raise NativeError("norm_conv: conv_w must be contiguous [taps, width] in the compute type, with the batch given")
         if taps > 1 and (tail is None or tail.dtype != torch.float32 or not tail.is_contiguous() or tuple(tail.shape[1:]) != (2, taps - 1, x.shape[1])):
             raise NativeError("norm_conv: tail must be contiguous float32 [slots, 2, taps - 1, width]")
         p.conv_w, p.taps, p.tail = conv_w.data_ptr(), taps, _ptr(tail)
@@ -471,10 +475,17 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
 MOE_ROWS_MAX_PAIRS = 64
 
 
-def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, grouped: Optional[bool] = None) -> torch.Tensor:
-    """The chosen experts' results, float32 [T * top, width] (rows of pass-through choices are not written).  w_gu [E, 2 ff,
-    width], w_down [E, width, ff].  Few pairs stream each chosen expert's weights once; many pairs in bfloat16 are sorted
-    by expert and go through the grouped tensor-core products."""
+def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, grouped=None):
+    """The chosen experts' results: (y [rows, width], row_of) where pair p = (token p // top, choice p % top) finds its result
+    in row row_of[p] of y (row_of None: row p); rows of pass-through choices are not written.  w_gu [E, 2 ff, width] (gate rows,
+    then up rows), w_down [E, width, ff].
+      grouped=False       the row kernels: every pair streams its expert's weights once (decoding; the 32-bit path); y float32
+      grouped="library"   many pairs in bfloat16: pairs sorted by expert on the device (`pcs_moe_plan`), their rows gathered
+                          (`pcs_moe_gather`), then the library's grouped product twice with `pcs_silu_mul` between; y bfloat16
+                          in the sorted order
+      grouped="own"       the same through this library's grouped tensor-core kernel (`pcs_moe_gemm`), activation in its
+                          epilogue, y float32 by pair
+    None chooses by size: the row kernels up to 64 pairs, otherwise the library's product (or this library's where torch has none)."""
     _cuda(h, idx, w_gu, w_down)
     dt = h.dtype
     _rows2d(h, dt, "moe_experts: h")
@@ -485,31 +496,47 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
         raise NativeError("moe_experts: weights [E, 2 ff, width] and [E, width, ff] in h's type, idx contiguous int32")
     T, top = idx.shape
     P = T * top
-    y = torch.empty(P, W, dtype=torch.float32, device=h.device)
-    act = torch.empty(P, ff, dtype=dt, device=h.device)
     can_group = dt == torch.bfloat16 and ff % 8 == 0 and W % 8 == 0 and (h.stride(0) * 2) % 16 == 0 and h.data_ptr() % 16 == 0
+    has_library = hasattr(torch.nn.functional, "grouped_mm")
+    if grouped is True:
+        grouped = "own"
     if grouped is None:
-        grouped = can_group and P > MOE_ROWS_MAX_PAIRS
+        grouped = ("library" if has_library else "own") if (can_group and P > MOE_ROWS_MAX_PAIRS) else False
     if grouped:
         if not can_group:
             raise NativeError("moe_experts: the grouped products need bfloat16 and sizes that are multiples of 8")
         lib = load()
         plan = torch.empty(int(lib.pcs_moe_plan_ints(P, E)), dtype=torch.int32, device=h.device)
         _check(lib.pcs_moe_plan(idx.data_ptr(), P, E, plan.data_ptr(), _stream()), "pcs_moe_plan")
-        _check(lib.pcs_moe_gemm(0, h.data_ptr(), h.stride(0), w_gu.data_ptr(), plan.data_ptr(), act.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
-        _check(lib.pcs_moe_gemm(1, act.data_ptr(), ff, w_down.data_ptr(), plan.data_ptr(), y.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
-        return y
+        if grouped == "own":
+            y = torch.empty(P, W, dtype=torch.float32, device=h.device)
+            act = torch.empty(P, ff, dtype=dt, device=h.device)
+            _check(lib.pcs_moe_gemm(0, h.data_ptr(), h.stride(0), w_gu.data_ptr(), plan.data_ptr(), act.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
+            _check(lib.pcs_moe_gemm(1, act.data_ptr(), ff, w_down.data_ptr(), plan.data_ptr(), y.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
+            return y, None
+        if grouped != "library" or not has_library:
+            raise NativeError(f"moe_experts: unknown grouped mode {grouped!r} (or torch has no grouped product)")
+        o_ends, o_rows = lib.pcs_moe_plan_part(0, P, E), lib.pcs_moe_plan_part(3, P, E)
+        ends, row_of = plan[o_ends:o_ends + E], plan[o_rows:o_rows + P]
+        a = torch.empty(P, W, dtype=dt, device=h.device)
+        _check(lib.pcs_moe_gather(h.data_ptr(), h.stride(0), plan.data_ptr(), a.data_ptr(), P, top, E, W, _stream()), "pcs_moe_gather")
+        gu = torch.nn.functional.grouped_mm(a, w_gu.transpose(1, 2), offs=ends)
+        y = torch.nn.functional.grouped_mm(silu_mul(gu, ff), w_down.transpose(1, 2), offs=ends)
+        return y, row_of
+    y = torch.empty(P, W, dtype=torch.float32, device=h.device)
+    act = torch.empty(P, ff, dtype=dt, device=h.device)
     _check(load().pcs_moe_rows_up(h.data_ptr(), h.stride(0), w_gu.data_ptr(), idx.data_ptr(), act.data_ptr(), P, top, E, ff, W, dtype_code(dt), _stream()),
            "pcs_moe_rows_up")
     _check(load().pcs_moe_rows_down(act.data_ptr(), w_down.data_ptr(), idx.data_ptr(), y.data_ptr(), P, E, ff, W, dtype_code(dt), _stream()),
            "pcs_moe_rows_down")
-    return y
+    return y, None
 
 
 def moe_combine(x: torch.Tensor, y: Optional[torch.Tensor], idx: torch.Tensor, wgt: torch.Tensor, h: torch.Tensor, n_experts: int, mult: float,
-                ys: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
-    """x += mult * (sum_k wgt[:, k] * (y of the choice, or h itself for a choice >= n_experts) + shared_gate * ys)."""
-    _cuda(x, y, idx, wgt, h, ys, shared_gate)
+                ys: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None, y_row: Optional[torch.Tensor] = None) -> None:
+    """x += mult * (sum_k wgt[:, k] * (y of the choice, or h itself for a choice >= n_experts) + shared_gate * ys).  y is float32 or
+    in h's type; `y_row` maps pair t * top + k to its row of y (None: the pair's own index)."""
+    _cuda(x, y, idx, wgt, h, ys, shared_gate, y_row)
     dt = h.dtype
     _rows2d(h, dt, "moe_combine: h")
     if x.dtype != torch.float32 or not x.is_contiguous() or x.shape != h.shape:
@@ -517,14 +544,18 @@ def moe_combine(x: torch.Tensor, y: Optional[torch.Tensor], idx: torch.Tensor, w
     T, top = idx.shape
     if idx.dtype != torch.int32 or wgt.dtype != torch.float32 or not (idx.is_contiguous() and wgt.is_contiguous()) or wgt.shape != idx.shape or T != x.shape[0]:
         raise NativeError("moe_combine: idx int32 and wgt float32 [T, top]")
-    if y is not None and (y.dtype != torch.float32 or not y.is_contiguous() or tuple(y.shape) != (T * top, x.shape[1])):
-        raise NativeError("moe_combine: y must be contiguous float32 [T * top, width]")
+    if y is not None and (y.dtype not in (torch.float32, dt) or not y.is_contiguous() or y.dim() != 2 or y.shape[1] != x.shape[1]
+                          or (y_row is None and y.shape[0] != T * top)):
+        raise NativeError("moe_combine: y must be contiguous [rows, width], float32 or in h's type")
+    if y_row is not None and (y_row.dtype != torch.int32 or not y_row.is_contiguous() or y_row.numel() != T * top):
+        raise NativeError("moe_combine: y_row must be contiguous int32 [T * top]")
     if ys is not None:
         _rows2d(ys, dt, "moe_combine: ys")
     p = pcs_combine_params()
     p.x, p.y, p.idx, p.wgt, p.h, p.h_stride = x.data_ptr(), _ptr(y), idx.data_ptr(), wgt.data_ptr(), h.data_ptr(), h.stride(0)
     p.ys, p.ys_stride, p.shared_gate, p.mult = _ptr(ys), ys.stride(0) if ys is not None else 0, _ptr(shared_gate), float(mult)
     p.n_tokens, p.width, p.top, p.n_experts, p.dtype = T, x.shape[1], top, int(n_experts), dtype_code(dt)
+    p.y_dtype, p.y_row = (PCS_F32 if (y is None or y.dtype == torch.float32) else dtype_code(dt)), _ptr(y_row)
     _check(load().pcs_moe_combine(C.byref(p), _stream()), "pcs_moe_combine")
 
 

@@ -331,7 +331,7 @@ def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: 
     out["like_attn_decode_full"] = gb(2.0 * G * (ctx + 1) * (D + V), ms)
     # norm + convolution: reads x (4 B, neighbours from L2) and writes h (2 B); like: gated norm + residual + next norm
     x, h = torch.randn(prompt, W, device=dev), torch.empty(prompt, W, device=dev, dtype=bf)
-    g1, cw, tail = torch.ones(1, device=dev, dtype=bf), (torch.randn(W, 4, device=dev) * 0.3).to(bf), torch.zeros(1, 2, 3, W, device=dev)
+    g1, cw, tail = torch.ones(1, device=dev, dtype=bf), (torch.randn(4, W, device=dev) * 0.3).to(bf), torch.zeros(1, 2, 3, W, device=dev)
     ms = timer(lambda: nsq.norm_conv(x, g1, 1e-5, h, conv_w=cw, tail=tail, batch=b))
     out["norm_conv"] = gb(prompt * W * 6.0, ms)
     y = torch.randn(prompt, W, device=dev).to(bf)
@@ -358,8 +358,10 @@ def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: 
     real = int((idx < E).sum())
     # the experts of a prompt: FLOPs = 6 ff W per real pair; like: the dense feed-forward's library products of the same FLOPs
     wgu, wdn = (torch.randn(E, 2 * ff, W, device=dev) * W ** -0.5).to(bf), (torch.randn(E, W, ff, device=dev) * ff ** -0.5).to(bf)
-    ms = timer(lambda: nsq.moe_experts(hb, idx, wgu, wdn, grouped=True))
-    out["moe_experts_prompt"] = dict(tf(6.0 * ff * W * real, ms), pairs=real)
+    ms = timer(lambda: nsq.moe_experts(hb, idx, wgu, wdn, grouped="library"))
+    out["moe_experts_prompt"] = dict(tf(6.0 * ff * W * real, ms), pairs=real, what="plan + gather + library grouped products + silu_mul")
+    ms = timer(lambda: nsq.moe_experts(hb, idx, wgu, wdn, grouped="own"))
+    out["moe_experts_prompt_own_kernel"] = tf(6.0 * ff * W * real, ms)
     rows = max(real, 1)
     xa, wa, wb2 = torch.randn(rows, W, device=dev).to(bf), wgu[0], wdn[0]
     ms = timer(lambda: torch.nn.functional.linear(torch.nn.functional.linear(xa, wa)[:, :ff], wb2))

@@ -79,20 +79,128 @@ __global__ void __launch_bounds__(256) norm_conv_kernel(const pcs_normconv_param
   for (int i = tid; i < W; i += 256) {
     const float gi = p.g_len == 1 ? g1 : ldf(g + i);
     const float u = x[i] * inv * gi;
-    float acc = u * (1.f + ldf(cw + static_cast<long long>(i) * p.taps + R));
+    float acc = u * (1.f + ldf(cw + static_cast<long long>(R) * W + i));
 #pragma unroll
     for (int j = 1; j < kMaxTaps; ++j) {
       if (j <= R && pos - j >= 0) {
         float uj;
         if (pos - j >= pos0) uj = x[i - static_cast<long long>(j) * W] * inv_prev[j] * gi;
         else uj = tail_r[static_cast<long long>(R - (pos0 - (pos - j))) * W + i];
-        acc = fmaf(ldf(cw + static_cast<long long>(i) * p.taps + R - j), uj, acc);
+        acc = fmaf(ldf(cw + static_cast<long long>(R - j) * W + i), uj, acc);
       }
     }
     stf(h + i, acc);
     if (last_row >= 0) tail_w[static_cast<long long>(last_row) * W + i] = u;
   }
   if (pos == pos0 + len - 1 && len < R) {  // rows that stay: new row r holds position pos0 + len - R + r = old row r + len
+    for (int r = 0; r < R - len; ++r)
+      for (int i = tid; i < W; i += 256) tail_w[static_cast<long long>(r) * W + i] = tail_r[static_cast<long long>(r + len) * W + i];
+  }
+}
+
+// The same for rows of at most 256 * PPT 16-byte pieces (pointers, strides and the width multiples of a piece) and at most four
+// taps: a thread keeps its pieces of the row and of the predecessors' rows in registers, every load is requested before the
+// first reduction, and the rows' sums of squares meet in ONE reduction.
+template <typename T, int PPT>
+__global__ void __launch_bounds__(256) norm_conv_vec_kernel(const pcs_normconv_params p) {
+  constexpr int N = Vec<T>::n, MR = 3;
+  __shared__ float red[MR + 1][9];
+  const int t = blockIdx.x, W = p.width, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float* x = p.x + static_cast<long long>(t) * W;
+  const T* g = static_cast<const T*>(p.g);
+  const T* cw = static_cast<const T*>(p.conv_w);
+  const int R = cw ? p.taps - 1 : 0;
+  int pos = 0, pos0 = 0, len = 1, slot = 0, par = 0;
+  if (cw) {
+    const int b = p.tok_seq[t];
+    pos = p.tok_pos[t]; slot = p.seq_slot[b]; pos0 = p.seq_pos0[b]; len = p.seq_len[b]; par = p.seq_par[b] & 1;
+  }
+  const float* tail_r = p.tail + (static_cast<long long>(slot) * 2 + par) * R * W;
+  float* tail_w = p.tail + (static_cast<long long>(slot) * 2 + (par ^ 1)) * R * W;
+  float xv[PPT][N], pv[MR][PPT][N], ss[MR + 1];
+#pragma unroll
+  for (int j = 0; j <= MR; ++j) ss[j] = 0.f;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    const int i = (tid + u * 256) * N;
+    if (i < W) {
+      ldx(x + i, xv[u]);
+      if (p.y) {
+        float yv[N];
+        ld16(static_cast<const T*>(p.y) + static_cast<long long>(t) * p.y_stride + i, yv);
+#pragma unroll
+        for (int e = 0; e < N; ++e) xv[u][e] = fmaf(p.y_mult, yv[e], xv[u][e]);
+        stx(x + i, xv[u]);
+      }
+#pragma unroll
+      for (int j = 1; j <= MR; ++j) {
+        if (j <= R && pos - j >= 0) {
+          if (pos - j >= pos0) ldx(x - static_cast<long long>(j) * W + i, pv[j - 1][u]);               // a row of this step: normed below
+          else ldx(tail_r + static_cast<long long>(R - (pos0 - (pos - j))) * W + i, pv[j - 1][u]);     // an earlier step's: normed already
+        } else {
+#pragma unroll
+          for (int e = 0; e < N; ++e) pv[j - 1][u][e] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) ss[0] = fmaf(xv[u][e], xv[u][e], ss[0]);
+#pragma unroll
+      for (int j = 1; j <= MR; ++j)
+#pragma unroll
+        for (int e = 0; e < N; ++e) ss[j] = fmaf(pv[j - 1][u][e], pv[j - 1][u][e], ss[j]);
+    }
+  }
+  if (p.h_out == nullptr) return;
+#pragma unroll
+  for (int j = 0; j <= MR; ++j) {
+    ss[j] = warp_sum(ss[j]);
+    if (lane == 0) red[j][warp] = ss[j];
+  }
+  __syncthreads();
+  float inv[MR + 1];
+#pragma unroll
+  for (int j = 0; j <= MR; ++j) {
+    float a = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) a += red[j][q];
+    inv[j] = 1.f / sqrtf(a / static_cast<float>(W) + p.eps);
+    if (j > 0 && !(pos - j >= pos0)) inv[j] = 1.f;   // rows from the tail (or before the start: zeros) are not normed again
+  }
+  const float g1 = p.g_len == 1 ? ldf(g) : 0.f;
+  const int last_row = pos - (pos0 + len - R);
+  T* h = static_cast<T*>(p.h_out) + static_cast<long long>(t) * W;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    const int i = (tid + u * 256) * N;
+    if (i < W) {
+      float gv[N], uv[N], o[N];
+      if (p.g_len == 1) {
+#pragma unroll
+        for (int e = 0; e < N; ++e) gv[e] = g1;
+      } else {
+        ld16(g + i, gv);
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) { uv[e] = xv[u][e] * inv[0] * gv[e]; o[e] = uv[e]; }
+      if (cw) {
+        float wv[N];
+        ld16(cw + static_cast<long long>(R) * W + i, wv);
+#pragma unroll
+        for (int e = 0; e < N; ++e) o[e] = uv[e] * (1.f + wv[e]);
+#pragma unroll
+        for (int j = 1; j <= MR; ++j)
+          if (j <= R) {
+            ld16(cw + static_cast<long long>(R - j) * W + i, wv);
+            const bool here = pos - j >= pos0;
+#pragma unroll
+            for (int e = 0; e < N; ++e) o[e] = fmaf(wv[e], pv[j - 1][u][e] * inv[j] * (here ? gv[e] : 1.f), o[e]);
+          }
+        if (last_row >= 0) stx(tail_w + static_cast<long long>(last_row) * W + i, uv);
+      }
+      st16(h + i, o);
+    }
+  }
+  if (cw && pos == pos0 + len - 1 && len < R) {
     for (int r = 0; r < R - len; ++r)
       for (int i = tid; i < W; i += 256) tail_w[static_cast<long long>(r) * W + i] = tail_r[static_cast<long long>(r + len) * W + i];
   }
@@ -129,6 +237,19 @@ PCS_API int pcs_norm_conv(const pcs_normconv_params* p, void* stream) {
                 "pcs_norm_conv: the convolution needs the tail and the batch description");
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int piece = p->dtype == PCS_BF16 ? 8 : 4;
+  const long long esz = p->dtype == PCS_BF16 ? 2 : 4;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = p->width % piece == 0 && p->width <= 512 * piece && al(p->x) && al(p->h_out) && al(p->tail) &&
+                   (p->y == nullptr || (al(p->y) && (p->y_stride * esz) % 16 == 0)) && (p->g_len == 1 || al(p->g)) && al(p->conv_w) &&
+                   (p->conv_w == nullptr || p->taps <= 4);
+  if (vec) {
+    if (p->width <= 256 * piece) PCS_DISPATCH(p->dtype, pcs::norm_conv_vec_kernel<T, 1><<<p->n_tokens, 256, 0, st>>>(*p));
+    else PCS_DISPATCH(p->dtype, pcs::norm_conv_vec_kernel<T, 2><<<p->n_tokens, 256, 0, st>>>(*p));
+    PCS_CHECK_CUDA(cudaGetLastError());
+    pcs::count_launch();
+    return PCS_OK;
+  }
   PCS_DISPATCH(p->dtype, pcs::norm_conv_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();

@@ -55,26 +55,9 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __re
 
 __host__ __device__ __forceinline__ bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
-template <typename T>
-__global__ void __launch_bounds__(256) moe_route_kernel(const pcs_route_params p) {
-  __shared__ float z[kMaxRouterOutputs];   // logits, then scores
-  __shared__ float c[kMaxRouterOutputs];   // choice scores (minus infinity once taken or not allowed)
-  __shared__ float gs[kMaxRouterOutputs];  // the groups' scores
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, E = p.n_outputs, K = p.width;
-  const T* h = static_cast<const T*>(p.h) + static_cast<long long>(t) * p.h_stride;
-  const T* wr = static_cast<const T*>(p.w_router);
-  const bool vec = K % Vec<T>::n == 0 && aligned16(h) && aligned16(wr) && (p.h_stride * sizeof(T)) % 16 == 0;
-  for (int e = warp; e < E; e += 8) {
-    const float d = warp_dot(h, wr + static_cast<long long>(e) * K, K, lane, vec);
-    if (lane == 0) z[e] = d;
-  }
-  if (p.w_sg && warp == 7) {
-    const T* ws = static_cast<const T*>(p.w_sg);
-    const float d = warp_dot(h, ws, K, lane, vec && aligned16(ws));
-    if (lane == 0) p.shared_gate[t] = sigmoidf_(d);
-  }
-  __syncthreads();
-  if (warp != 0) return;
+// One warp, one token: z holds the router's logits on entry.  Softmax, choice scores, group limits and `top` arg-max rounds.
+__device__ __forceinline__ void route_select(const pcs_route_params& p, int t, int lane, float* z, float* c, float* gs) {
+  const int E = p.n_outputs;
   float m = -INFINITY;
   for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
   m = warp_max(m);
@@ -123,6 +106,57 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const pcs_route_params p
     }
     __syncwarp();
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_route_kernel(const pcs_route_params p) {
+  __shared__ float z[kMaxRouterOutputs];   // logits, then scores
+  __shared__ float c[kMaxRouterOutputs];   // choice scores (minus infinity once taken or not allowed)
+  __shared__ float gs[kMaxRouterOutputs];  // the groups' scores
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, E = p.n_outputs, K = p.width;
+  const T* h = static_cast<const T*>(p.h) + static_cast<long long>(t) * p.h_stride;
+  const T* wr = static_cast<const T*>(p.w_router);
+  const bool vec = K % Vec<T>::n == 0 && aligned16(h) && aligned16(wr) && (p.h_stride * sizeof(T)) % 16 == 0;
+  for (int e = warp; e < E; e += 8) {
+    const float d = warp_dot(h, wr + static_cast<long long>(e) * K, K, lane, vec);
+    if (lane == 0) z[e] = d;
+  }
+  if (p.w_sg && warp == 7) {
+    const T* ws = static_cast<const T*>(p.w_sg);
+    const float d = warp_dot(h, ws, K, lane, vec && aligned16(ws));
+    if (lane == 0) p.shared_gate[t] = sigmoidf_(d);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  route_select(p, t, lane, z, c, gs);
+}
+
+// The same with one WARP per token (many tokens): the eight warps of a block walk the router's rows together, so a row comes
+// from L2 once per eight tokens; each warp then selects for its own token.  Results equal the block-per-token kernel's.
+constexpr int kWarpRouteOutputs = 256;
+template <typename T>
+__global__ void __launch_bounds__(256) moe_route_warp_kernel(const pcs_route_params p) {
+  __shared__ float buf[8][4 * kWarpRouteOutputs];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, E = p.n_outputs, K = p.width;
+  const int t = blockIdx.x * 8 + warp;
+  if (t >= p.n_tokens) return;
+  float* z = buf[warp];
+  float* c = z + kWarpRouteOutputs;
+  float* gs = c + kWarpRouteOutputs;
+  const T* h = static_cast<const T*>(p.h) + static_cast<long long>(t) * p.h_stride;
+  const T* wr = static_cast<const T*>(p.w_router);
+  const bool vec = K % Vec<T>::n == 0 && aligned16(h) && aligned16(wr) && (p.h_stride * sizeof(T)) % 16 == 0;
+  for (int e = 0; e < E; ++e) {
+    const float d = warp_dot(h, wr + static_cast<long long>(e) * K, K, lane, vec);
+    if (lane == 0) z[e] = d;
+  }
+  if (p.w_sg) {
+    const T* ws = static_cast<const T*>(p.w_sg);
+    const float d = warp_dot(h, ws, K, lane, vec && aligned16(ws));
+    if (lane == 0) p.shared_gate[t] = sigmoidf_(d);
+  }
+  __syncwarp();
+  route_select(p, t, lane, z, c, gs);
 }
 
 // block = (pair, 8 features); warp w owns features n0 + 2w, n0 + 2w + 1
@@ -175,7 +209,13 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const pcs_combine_para
     for (int k = 0; k < p.top; ++k) {
       const long long pr = static_cast<long long>(t) * p.top + k;
       const int e = p.idx[pr];
-      const float v = e < p.n_experts ? p.y[pr * W + i] : ldf(h + i);
+      float v;
+      if (e < p.n_experts) {
+        const long long row = p.y_row ? p.y_row[pr] : pr;
+        v = p.y_dtype == PCS_F32 ? static_cast<const float*>(p.y)[row * W + i] : ldf(static_cast<const T*>(p.y) + row * W + i);
+      } else {
+        v = ldf(h + i);
+      }
       a = fmaf(p.wgt[pr], v, a);
     }
     if (ys) a = fmaf(sg, ldf(ys + i), a);
@@ -207,7 +247,10 @@ PCS_API int pcs_moe_route(const pcs_route_params* p, void* stream) {
   PCS_REQUIRE(p->top <= p->keep_groups * (p->n_outputs / p->n_groups), "pcs_moe_route: top %d exceeds the outputs of the kept groups", p->top);
   PCS_REQUIRE(p->w_sg == nullptr || p->shared_gate != nullptr, "pcs_moe_route: the shared gate needs its output");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  PCS_DISPATCH(p->dtype, pcs::moe_route_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
+  if (p->n_tokens >= 64 && p->n_outputs <= pcs::kWarpRouteOutputs)
+    PCS_DISPATCH(p->dtype, pcs::moe_route_warp_kernel<T><<<(p->n_tokens + 7) / 8, 256, 0, st>>>(*p));
+  else
+    PCS_DISPATCH(p->dtype, pcs::moe_route_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;

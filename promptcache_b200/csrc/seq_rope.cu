@@ -1,6 +1,7 @@
 // Rotation of queries and keys by position, unit-RMS values, and the append of K/V rows to the slot pool.
 //
-// One block per token.  A coordinate pair of a head, (2i, 2i+1) or (i, i + rot_dims/2), turns by the angle pos * freqs[i]:
+// One block per token; the token's sines and cosines are formed once, in shared memory, for all heads.  A coordinate pair
+// of a head, (2i, 2i+1) or (i, i + rot_dims/2), turns by the angle pos * freqs[i]:
 // (u, v) -> (u cos a - v sin a, v cos a + u sin a).  The frequency table comes from the host in 64-bit, so any spacing or
 // rescaling of the frequencies is the caller's; the angle is formed and reduced modulo 2 pi in 64-bit (three operations) and
 // its sine and cosine are taken in 32-bit of an argument in [-pi, pi], which keeps them exact to 32-bit rounding at any position.
@@ -15,9 +16,11 @@ __device__ __forceinline__ void angle_sincos(int pos, double f, float* s, float*
   sincosf(static_cast<float>(r), s, c);
 }
 
-// src: `heads` heads of `dim` coordinates; dst(head) gives the head's destination
+constexpr int kMaxRotPairs = 256;  // rot_dims <= 512
+
+// src: `heads` heads of `dim` coordinates; dst(head) gives the head's destination; sc: the token's (sin, cos) per pair
 template <typename T, typename Dst>
-__device__ __forceinline__ void rotate_heads(const T* src, int heads, int dim, int rot, int interleaved, const double* freqs, int pos, Dst dst) {
+__device__ __forceinline__ void rotate_heads(const T* src, int heads, int dim, int rot, int interleaved, const float2* sc, Dst dst) {
   const int half = rot / 2, per = half + (dim - rot);  // work items per head: rotated pairs, then single coordinates
   for (int e = threadIdx.x; e < heads * per; e += blockDim.x) {
     const int hd = e / per, i = e - hd * per;
@@ -25,8 +28,7 @@ __device__ __forceinline__ void rotate_heads(const T* src, int heads, int dim, i
     T* d = dst(hd);
     if (i < half) {
       const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
-      float sn, cs;
-      angle_sincos(pos, freqs[i], &sn, &cs);
+      const float sn = sc[i].x, cs = sc[i].y;
       const float u = ldf(s + a), v = ldf(s + b);
       stf(d + a, u * cs - v * sn);
       stf(d + b, v * cs + u * sn);
@@ -43,11 +45,14 @@ __global__ void __launch_bounds__(256) rope_kv_prep_kernel(const pcs_rope_params
   const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
   const T* row = static_cast<const T*>(p.qkv) + static_cast<long long>(t) * p.row_stride;
   const int D = p.dim, V = p.vdim;
+  __shared__ float2 sc[kMaxRotPairs];  // the token's angles, shared by all heads
+  for (int i = threadIdx.x; i < p.rot_dims / 2; i += blockDim.x) angle_sincos(pos, p.freqs[i], &sc[i].x, &sc[i].y);
+  __syncthreads();
   T* qo = static_cast<T*>(p.q_out) + static_cast<long long>(t) * p.n_heads * D;
-  rotate_heads(row + p.q_off, p.n_heads, D, p.rot_dims, p.interleaved, p.freqs, pos, [&](int hd) { return qo + hd * D; });
+  rotate_heads(row + p.q_off, p.n_heads, D, p.rot_dims, p.interleaved, sc, [&](int hd) { return qo + hd * D; });
   if (p.k_off < 0) return;
   T* kp = static_cast<T*>(p.k_pool) + static_cast<long long>(slot) * p.n_kv_heads * p.cap * D;
-  rotate_heads(row + p.k_off, p.n_kv_heads, D, p.rot_dims, p.interleaved, p.freqs, pos,
+  rotate_heads(row + p.k_off, p.n_kv_heads, D, p.rot_dims, p.interleaved, sc,
                [&](int hd) { return kp + (static_cast<long long>(hd) * p.cap + pos) * D; });
   T* vp = static_cast<T*>(p.v_pool) + static_cast<long long>(slot) * p.n_kv_heads * p.cap * V;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -73,8 +78,8 @@ PCS_API int pcs_rope_kv_prep(const pcs_rope_params* p, void* stream) {
   PCS_REQUIRE(p->qkv && p->q_out && p->tok_seq && p->tok_pos && p->seq_slot, "pcs_rope_kv_prep: null tensor");
   PCS_REQUIRE(p->k_off < 0 || (p->k_pool && p->v_pool && p->cap > 0), "pcs_rope_kv_prep: keys and values need their pools");
   PCS_REQUIRE(p->n_heads > 0 && p->n_kv_heads > 0 && p->dim > 0 && p->vdim > 0, "pcs_rope_kv_prep: bad sizes");
-  PCS_REQUIRE(p->rot_dims >= 0 && p->rot_dims <= p->dim && p->rot_dims % 2 == 0 && (p->rot_dims == 0 || p->freqs),
-              "pcs_rope_kv_prep: rot_dims %d must be even, at most dim %d, with a frequency table", p->rot_dims, p->dim);
+  PCS_REQUIRE(p->rot_dims >= 0 && p->rot_dims <= p->dim && p->rot_dims % 2 == 0 && (p->rot_dims == 0 || p->freqs) && p->rot_dims <= 2 * pcs::kMaxRotPairs,
+              "pcs_rope_kv_prep: rot_dims %d must be even, at most dim %d and %d, with a frequency table", p->rot_dims, p->dim, 2 * pcs::kMaxRotPairs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   PCS_DISPATCH(p->dtype, pcs::rope_kv_prep_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());

@@ -119,7 +119,8 @@ class RaritarForCausalLM(SlotPoolCausalLM):
                                          device=dev) if rd else None,
                    "scale": float(m.get("scale", D ** -0.5)), "softcap": float(m.get("softcap") or 0.0),
                    "window": int(mask.get("size", 0)), "keep_first": int(mask.get("keep_first", 0)),
-                   "norm1": get(p + "norm1").reshape(1), "canon": get(p + "canon1") if config.taps else None, "w_o": get(p + "mix.o")}
+                   "norm1": get(p + "norm1").reshape(1), "canon": get(p + "canon1").t().contiguous() if config.taps else None,   # [taps, width] for the kernel
+                   "w_o": get(p + "mix.o")}
             if src is None:
                 blk.update(kv_src=i, w_in=torch.cat([get(p + "mix.q"), get(p + "mix.k"), get(p + "mix.v")], 0).contiguous(),
                            offs=(0, H * D, (H + G) * D), kv=KVSpec(G, D, V))
@@ -156,7 +157,7 @@ class RaritarForCausalLM(SlotPoolCausalLM):
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
         self.attn_impl = 0
-        self.moe_grouped: Optional[bool] = None   # None: by size; True / False force the grouped products / the row kernels
+        self.moe_grouped = None   # None: by size; False / "library" / "own" force the row kernels or one of the grouped products
         self._init_runtime(dev, max_tokens)
 
     def state_specs(self):
@@ -205,12 +206,12 @@ class RaritarForCausalLM(SlotPoolCausalLM):
                 nsq.norm_conv(x, blk["norm2"], eps, h, y=y, y_mult=m)       # x += m * y;  h = g2 * rms(x)
                 idx, wgt, sg = nsq.moe_route(h, blk["w_router"], blk["correction"], blk.get("w_sg") if blk["shared"] else None, blk["top"],
                                              blk["n_groups"], blk["keep_groups"])
-                ye = nsq.moe_experts(h, idx, blk["w_gu"], blk["w_down"], grouped=self.moe_grouped) if blk["n_experts"] else None
+                ye, rows_e = nsq.moe_experts(h, idx, blk["w_gu"], blk["w_down"], grouped=self.moe_grouped) if blk["n_experts"] else (None, None)
                 ys = None
                 if blk["shared"]:
                     gu = nsq.linear(h, blk["ws_gu"])
                     ys = nsq.linear(nsq.silu_mul(gu, gu.shape[1] // 2), blk["ws_down"])
-                nsq.moe_combine(x, ye, idx, wgt, h, blk["n_experts"], m, ys=ys, shared_gate=sg)
+                nsq.moe_combine(x, ye, idx, wgt, h, blk["n_experts"], m, ys=ys, shared_gate=sg, y_row=rows_e)
             else:
                 nsq.norm_conv(x, None, eps, None, y=y, y_mult=m)
             if self.layer_trace is not None:

@@ -118,7 +118,7 @@ def test_norm_and_time_convolution_in_portions(nsq, taps, width):
             x = torch.cat([xs[b][pos[b]:pos[b] + l] for b, l in zip(entries, lens)])
             h = torch.empty(x.shape[0], width, device=DEV)
             b_ = batch_of(nsq, [2 if b == 0 else 0 for b in entries], [pos[b] for b in entries], lens, [steps[b] & 1 for b in entries])
-            nsq.norm_conv(dev(x), dev(g), eps, h, conv_w=dev(w), tail=tail, batch=b_)
+            nsq.norm_conv(dev(x), dev(g), eps, h, conv_w=dev(w.t()), tail=tail, batch=b_)
             o = 0
             for b, l in zip(entries, lens):
                 got[b].append(h[o:o + l].cpu())
@@ -254,7 +254,7 @@ def test_one_key_decides_at_every_edge(nsq, dtype):
 @pytest.mark.parametrize("E,I,top,groups,keep", [(6, 2, 3, 4, 2), (8, 0, 2, 1, 1), (5, 1, 2, 3, 1), (4, 4, 4, 2, 1), (64, 0, 8, 8, 3), (3, 0, 3, 1, 1)])
 def test_router(nsq, E, I, top, groups, keep):
     torch.manual_seed(E * 7 + top)
-    T, W = 50, 48
+    T, W = 100, 48                                        # many tokens: one warp per token; few (below): one block per token
     h = torch.randn(T, W, dtype=F64)
     wr = torch.randn(E + I, W, dtype=F64) * 0.5
     corr = torch.randn(E + I, dtype=F64) * 0.2 - 0.3      # negative choice scores: a masked output must not win as "0"
@@ -266,6 +266,8 @@ def test_router(nsq, E, I, top, groups, keep):
         chosen, ws = O.route(z[t], corr, top, groups, keep)
         assert idx[t].tolist() == chosen, f"token {t}: chose {idx[t].tolist()}, oracle {chosen}"
         close(wgt[t], torch.stack(ws), 1e-5, "router weights")
+    idx5, wgt5, sg5 = nsq.moe_route(dev(h[:5]), dev(wr), dev(corr), dev(wsg), top, groups, keep)
+    assert torch.equal(idx5, idx[:5]) and torch.equal(wgt5, wgt[:5]) and torch.equal(sg5, sg[:5])
     idx2, wgt2, none = nsq.moe_route(dev(h), dev(wr), None, None, top, groups, keep)
     assert none is None
     chosen, _ = O.route(z[0], torch.zeros(E + I, dtype=F64), top, groups, keep)
@@ -297,17 +299,32 @@ def test_experts_rows_grouped_and_combine(nsq, T, ff, W):
             if e < E:
                 want[t * top + k_] = O.gated_ff(Wt, f"e{e}.", h[t:t + 1])[0]
                 real[t * top + k_] = True
-    y32 = nsq.moe_experts(dev(h), idx.to(DEV), dev(w_gu), dev(w_dn), grouped=False)
-    close(y32[real.to(DEV)], want[real], 1e-5, "row kernels, 32-bit")
-    yb = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=False)
-    close_rms(yb[real.to(DEV)], want[real], 4e-3, "row kernels, bfloat16")
+    rd = real.to(DEV)
+    y32, none = nsq.moe_experts(dev(h), idx.to(DEV), dev(w_gu), dev(w_dn), grouped=False)
+    assert none is None
+    close(y32[rd], want[real], 1e-5, "row kernels, 32-bit")
+    yb, _ = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=False)
+    close_rms(yb[rd], want[real], 4e-3, "row kernels, bfloat16")
     if ff % 8 or W % 8:                                   # sizes the 16-byte copies cannot take stay with the row kernels
-        with pytest.raises(nsq.NativeError):
-            nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=True)
+        for mode in ("own", "library"):
+            with pytest.raises(nsq.NativeError):
+                nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=mode)
     else:
-        yg = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=True)
-        close_rms(yg[real.to(DEV)], want[real], 4e-3, "grouped products")
-        close_rms(yg[real.to(DEV)], yb[real.to(DEV)], 2e-3, "grouped products against the row kernels")
+        yg, none = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped="own")
+        assert none is None
+        close_rms(yg[rd], want[real], 4e-3, "own grouped products")
+        close_rms(yg[rd], yb[rd], 2e-3, "own grouped products against the row kernels")
+        yl, row_of = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped="library")
+        assert bool((row_of[rd] >= 0).all()) and bool((row_of[~rd] == -1).all())
+        assert sorted(row_of[rd].tolist()) == list(range(int(real.sum())))      # the sort is a permutation of the real pairs
+        e_sorted = idx.flatten()[real][torch.argsort(row_of[rd].cpu())]
+        assert bool((e_sorted[1:] >= e_sorted[:-1]).all())                      # ... by expert
+        close_rms(yl[row_of[rd].long()], want[real], 8e-3, "library grouped products on sorted rows")
+        xa, xb = torch.zeros(T, W, device=DEV), torch.zeros(T, W, device=DEV)
+        ones = torch.ones(T, top, device=DEV)
+        nsq.moe_combine(xa, yl, idx.to(DEV), ones, dev(h, BF16), E, 1.0, y_row=row_of)
+        nsq.moe_combine(xb, yg, idx.to(DEV), ones, dev(h, BF16), E, 1.0)
+        close_rms(xa, xb, 8e-3, "weighted sum through the row map")
     # the weighted sum with pass-through outputs and the gated shared expert
     x = torch.randn(T, W, dtype=F64)
     wgt, sg, ys = torch.rand(T, top, dtype=F64), torch.rand(T, dtype=F64), torch.randn(T, W, dtype=F64)
