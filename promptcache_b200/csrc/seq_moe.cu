@@ -35,22 +35,37 @@ __device__ __forceinline__ int warp_argmax(const float* c, int n, int lane, floa
   return bi;
 }
 
+// lanes share K in 16-byte pieces; four independent partial sums per lane (pieces lane, lane + 32, ... go round them), so
+// that four loads of each operand are in flight and no sum waits for the one before.  The order depends on K alone.
 template <typename T>
 __device__ __forceinline__ float warp_dot(const T* __restrict__ a, const T* __restrict__ b, int K, int lane, bool vec) {
   constexpr int N = Vec<T>::n;
-  float s = 0.f;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   if (vec) {
-    for (int k = lane * N; k < K; k += 32 * N) {
+    int k = lane * N;
+    for (; k + 96 * N < K; k += 128 * N) {
+      float a0[N], a1[N], a2[N], a3[N], b0[N], b1[N], b2[N], b3[N];
+      ld16(a + k, a0); ld16(a + k + 32 * N, a1); ld16(a + k + 64 * N, a2); ld16(a + k + 96 * N, a3);
+      ld16(b + k, b0); ld16(b + k + 32 * N, b1); ld16(b + k + 64 * N, b2); ld16(b + k + 96 * N, b3);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        s0 = fmaf(a0[e], b0[e], s0);
+        s1 = fmaf(a1[e], b1[e], s1);
+        s2 = fmaf(a2[e], b2[e], s2);
+        s3 = fmaf(a3[e], b3[e], s3);
+      }
+    }
+    for (; k < K; k += 32 * N) {
       float av[N], bv[N];
       ld16(a + k, av);
       ld16(b + k, bv);
 #pragma unroll
-      for (int e = 0; e < N; ++e) s = fmaf(av[e], bv[e], s);
+      for (int e = 0; e < N; ++e) s0 = fmaf(av[e], bv[e], s0);
     }
   } else {
-    for (int k = lane; k < K; k += 32) s = fmaf(ldf(a + k), ldf(b + k), s);
+    for (int k = lane; k < K; k += 32) s0 = fmaf(ldf(a + k), ldf(b + k), s0);
   }
-  return warp_sum(s);
+  return warp_sum((s0 + s1) + (s2 + s3));
 }
 
 __host__ __device__ __forceinline__ bool aligned16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
@@ -197,40 +212,85 @@ __global__ void __launch_bounds__(128) moe_rows_down_kernel(const T* __restrict_
   }
 }
 
-template <typename T>
+constexpr int kCombineMaxTop = 64;
+
+// One block per token.  The token's choices (weight, row of y or "the input itself") are read once into shared memory; the
+// channels then go in 16-byte pieces where the pointers allow.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const pcs_combine_params p) {
+  constexpr int N = Vec<T>::n;
+  __shared__ float w_s[kCombineMaxTop];
+  __shared__ long long row_s[kCombineMaxTop];   // -1: a pass-through choice
   const int t = blockIdx.x, W = p.width;
+  if (threadIdx.x < p.top) {
+    const long long pr = static_cast<long long>(t) * p.top + threadIdx.x;
+    w_s[threadIdx.x] = p.wgt[pr];
+    row_s[threadIdx.x] = p.idx[pr] < p.n_experts ? (p.y_row ? static_cast<long long>(p.y_row[pr]) : pr) : -1;
+  }
+  __syncthreads();
   float* x = p.x + static_cast<long long>(t) * W;
   const T* h = static_cast<const T*>(p.h) + static_cast<long long>(t) * p.h_stride;
   const T* ys = p.ys ? static_cast<const T*>(p.ys) + static_cast<long long>(t) * p.ys_stride : nullptr;
   const float sg = (ys && p.shared_gate) ? p.shared_gate[t] : 1.f;
-  for (int i = threadIdx.x; i < W; i += 256) {
-    float a = 0.f;
-    for (int k = 0; k < p.top; ++k) {
-      const long long pr = static_cast<long long>(t) * p.top + k;
-      const int e = p.idx[pr];
-      float v;
-      if (e < p.n_experts) {
-        const long long row = p.y_row ? p.y_row[pr] : pr;
-        v = p.y_dtype == PCS_F32 ? static_cast<const float*>(p.y)[row * W + i] : ldf(static_cast<const T*>(p.y) + row * W + i);
-      } else {
-        v = ldf(h + i);
+  const bool y32 = p.y_dtype == PCS_F32;
+  if (VEC) {
+    for (int i = threadIdx.x * N; i < W; i += 256 * N) {
+      float a[N], v[N], xv[N];
+#pragma unroll
+      for (int e = 0; e < N; ++e) a[e] = 0.f;
+      for (int k = 0; k < p.top; ++k) {
+        const long long row = row_s[k];
+        if (row < 0) ld16(h + i, v);
+        else if (y32) ldx(static_cast<const float*>(p.y) + row * W + i, v);
+        else ld16(static_cast<const T*>(p.y) + row * W + i, v);
+        const float w = w_s[k];
+#pragma unroll
+        for (int e = 0; e < N; ++e) a[e] = fmaf(w, v[e], a[e]);
       }
-      a = fmaf(p.wgt[pr], v, a);
+      if (ys) {
+        ld16(ys + i, v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) a[e] = fmaf(sg, v[e], a[e]);
+      }
+      ldx(x + i, xv);
+#pragma unroll
+      for (int e = 0; e < N; ++e) xv[e] = fmaf(p.mult, a[e], xv[e]);
+      stx(x + i, xv);
     }
-    if (ys) a = fmaf(sg, ldf(ys + i), a);
-    x[i] = fmaf(p.mult, a, x[i]);
+  } else {
+    for (int i = threadIdx.x; i < W; i += 256) {
+      float a = 0.f;
+      for (int k = 0; k < p.top; ++k) {
+        const long long row = row_s[k];
+        const float v = row < 0 ? ldf(h + i) : (y32 ? static_cast<const float*>(p.y)[row * W + i] : ldf(static_cast<const T*>(p.y) + row * W + i));
+        a = fmaf(w_s[k], v, a);
+      }
+      if (ys) a = fmaf(sg, ldf(ys + i), a);
+      x[i] = fmaf(p.mult, a, x[i]);
+    }
   }
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, long long gu_stride, T* __restrict__ out, int ff) {
+  constexpr int N = Vec<T>::n;
   const int r = blockIdx.x;
   const T* g = gu + r * gu_stride;
   T* o = out + static_cast<long long>(r) * ff;
-  for (int i = blockIdx.y * 256 + threadIdx.x; i < ff; i += gridDim.y * 256) {
-    const float a = ldf(g + i);
-    stf(o + i, a * sigmoidf_(a) * ldf(g + ff + i));
+  if (VEC) {
+    for (int i = (blockIdx.y * 256 + threadIdx.x) * N; i < ff; i += gridDim.y * 256 * N) {
+      float a[N], u[N];
+      ld16(g + i, a);
+      ld16(g + ff + i, u);
+#pragma unroll
+      for (int e = 0; e < N; ++e) a[e] = a[e] * sigmoidf_(a[e]) * u[e];
+      st16(o + i, a);
+    }
+  } else {
+    for (int i = blockIdx.y * 256 + threadIdx.x; i < ff; i += gridDim.y * 256) {
+      const float a = ldf(g + i);
+      stf(o + i, a * sigmoidf_(a) * ldf(g + ff + i));
+    }
   }
 }
 
@@ -291,8 +351,14 @@ PCS_API int pcs_moe_combine(const pcs_combine_params* p, void* stream) {
   if (p->n_tokens == 0) return PCS_OK;
   PCS_REQUIRE(p->x && p->idx && p->wgt && p->h && p->n_tokens > 0 && p->width > 0 && p->top > 0, "pcs_moe_combine: bad arguments");
   PCS_REQUIRE(p->y || p->n_experts == 0, "pcs_moe_combine: expert results missing");
+  PCS_REQUIRE(p->top <= pcs::kCombineMaxTop, "pcs_moe_combine: top %d exceeds %d", p->top, pcs::kCombineMaxTop);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  PCS_DISPATCH(p->dtype, pcs::moe_combine_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
+  const int piece = p->dtype == PCS_BF16 ? 8 : 4;
+  const long long esz = p->dtype == PCS_BF16 ? 2 : 4;
+  const bool vec = p->width % piece == 0 && pcs::aligned16(p->x) && pcs::aligned16(p->y) && pcs::aligned16(p->h) && (p->h_stride * esz) % 16 == 0 &&
+                   (p->ys == nullptr || (pcs::aligned16(p->ys) && (p->ys_stride * esz) % 16 == 0));
+  if (vec) PCS_DISPATCH(p->dtype, (pcs::moe_combine_kernel<T, true><<<p->n_tokens, 256, 0, st>>>(*p)));
+  else PCS_DISPATCH(p->dtype, (pcs::moe_combine_kernel<T, false><<<p->n_tokens, 256, 0, st>>>(*p)));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
@@ -302,8 +368,12 @@ PCS_API int pcs_silu_mul(const void* gu, int64_t gu_stride, void* out, int n_row
   if (n_rows == 0 || ff == 0) return PCS_OK;
   PCS_REQUIRE(gu && out && n_rows > 0 && ff > 0, "pcs_silu_mul: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  dim3 grid(n_rows, (ff + 1023) / 1024);
-  PCS_DISPATCH(dtype, pcs::silu_mul_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff));
+  const int piece = dtype == PCS_BF16 ? 8 : 4;
+  const long long esz = dtype == PCS_BF16 ? 2 : 4;
+  const bool vec = ff % piece == 0 && (gu_stride * esz) % 16 == 0 && pcs::aligned16(gu) && pcs::aligned16(out);
+  dim3 grid(n_rows, vec ? (ff / piece + 255) / 256 : (ff + 1023) / 1024);
+  if (vec) PCS_DISPATCH(dtype, (pcs::silu_mul_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff)));
+  else PCS_DISPATCH(dtype, (pcs::silu_mul_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff)));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
