@@ -502,6 +502,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
         grouped = "own"
     if grouped is None:
         grouped = ("library" if has_library else "own") if (can_group and P > MOE_ROWS_MAX_PAIRS) else False
+    if grouped == "own" and not can_group and P <= 256:
+        grouped = False
     if grouped:
         if not can_group:
             raise NativeError("moe_experts: the grouped products need bfloat16 and sizes that are multiples of 8")

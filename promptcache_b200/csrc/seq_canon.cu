@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) embed_bigram_kernel(const T* __restrict__
   for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = ldf(e + i) + ldf(b + i);
 }
 
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256) norm_conv_kernel(const pcs_normconv_params p) {

@@ -206,7 +206,11 @@ class RaritarForCausalLM(SlotPoolCausalLM):
                 nsq.norm_conv(x, blk["norm2"], eps, h, y=y, y_mult=m)       # x += m * y;  h = g2 * rms(x)
                 idx, wgt, sg = nsq.moe_route(h, blk["w_router"], blk["correction"], blk.get("w_sg") if blk["shared"] else None, blk["top"],
                                              blk["n_groups"], blk["keep_groups"])
-                ye, rows_e = nsq.moe_experts(h, idx, blk["w_gu"], blk["w_down"], grouped=self.moe_grouped) if blk["n_experts"] else (None, None)
+                mode = self.moe_grouped
+                if mode is None and torch.cuda.is_current_stream_capturing():
+                    # a recorded decoding step keeps to this library's own kernels, whatever the batch size
+                    mode = False if T * blk["top"] <= 256 else "own"
+                ye, rows_e = nsq.moe_experts(h, idx, blk["w_gu"], blk["w_down"], grouped=mode) if blk["n_experts"] else (None, None)
                 ys = None
                 if blk["shared"]:
                     gu = nsq.linear(h, blk["ws_gu"])

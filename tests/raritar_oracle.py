@@ -76,10 +76,10 @@ def attention_core(q, k, v, scale, softcap, window, keep_first):
     T, H, _ = q.shape
     G = k.shape[1]
     out = torch.zeros(T, H, v.shape[-1], dtype=F64)
-    for h in range(H):
-        g = h // (H // G)
-        for i in range(T):
-            js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
+    for i in range(T):
+        js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
+        for h in range(H):
+            g = h // (H // G)
             s = (k[js, g] @ q[i, h]) * scale
             if softcap:
                 s = softcap * torch.tanh(s / softcap)

@@ -95,7 +95,7 @@ def test_pair_embedding(nsq):
     close(out[1:], table[toks[1:]] + pair[rows], 1e-6, "pair embedding, large multipliers")
 
 
-@pytest.mark.parametrize("taps,width", [(4, 40), (2, 33), (1, 16), (8, 24)])
+@pytest.mark.parametrize("taps,width", [(4, 40), (2, 33), (1, 16), (8, 24), (4, 1536), (3, 2052)])
 def test_norm_and_time_convolution_in_portions(nsq, taps, width):
     """Whole sequence at once against portions of every small size, through a dirty reused slot, two sequences interleaved."""
     torch.manual_seed(taps)
@@ -306,9 +306,8 @@ def test_experts_rows_grouped_and_combine(nsq, T, ff, W):
     yb, _ = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=False)
     close_rms(yb[rd], want[real], 4e-3, "row kernels, bfloat16")
     if ff % 8 or W % 8:                                   # sizes the 16-byte copies cannot take stay with the row kernels
-        for mode in ("own", "library"):
-            with pytest.raises(nsq.NativeError):
-                nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped=mode)
+        with pytest.raises(nsq.NativeError):
+            nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped="library")
     else:
         yg, none = nsq.moe_experts(dev(h, BF16), idx.to(DEV), dev(w_gu, BF16), dev(w_dn, BF16), grouped="own")
         assert none is None
@@ -351,11 +350,17 @@ def layer_sets():
                     experts=4, top=2, groups=(1, 1), shared_ff=0),
                   A(kv_from=0, window=5, keep_first=1), A(kv_from=0, mlp=False), A(heads=1, kv_heads=1, dim=24, vdim=8, rot_dims=24, window=1000,
                                                                                    experts=2, identity=3, top=2, groups=(5, 3), ff=8, shared_ff=40)],
+        # sizes that are not multiples of the 16-byte pieces: every kernel's plain path
+        "odd": [A(heads=3, kv_heads=1, dim=12, vdim=20, rot_dims=6, window=6, keep_first=2, experts=3, identity=1, top=2, groups=(2, 1), ff=20,
+                  shared_ff=12),
+                A(heads=3, kv_heads=1, dim=12, vdim=20, rot_dims=6, window=11, keep_first=0, kv_from=0, experts=5, identity=0, top=3,
+                  groups=(1, 1), ff=12, shared_ff=0)],
         "shared_first": [A(window=9, keep_first=2, top=1), A(kv_from=0, window=9, keep_first=2), A(kv_from=0, window=30, keep_first=0)],
     }
 
 
-@pytest.mark.parametrize("name,taps,buckets,width", [("mixed", 4, 53, 40), ("mixed", 2, 0, 24), ("shared_first", 0, 7, 64), ("shared_first", 3, 1, 40)])
+@pytest.mark.parametrize("name,taps,buckets,width", [("mixed", 4, 53, 40), ("mixed", 2, 0, 24), ("shared_first", 0, 7, 64), ("shared_first", 3, 1, 40), ("odd", 5, 10, 36),
+                                                      ("odd", 9, 3, 30)])
 def test_model_whole_prompt_against_oracle(tmp_path, name, taps, buckets, width):
     cfg = O.make_config(layer_sets()[name], width=width, taps=taps, buckets=buckets)
     W = O.random_model(cfg, seed=width)
@@ -446,6 +451,32 @@ def test_long_decoding_past_window_and_pool_growth(tmp_path):
                 other.free()
             out.append(m.step([(seq, [toks[p]])]))
     close(torch.cat(out), want, 5e-5, "long decoding")
+
+
+def test_medium_model_long_prompt(tmp_path):
+    """Sizes at which the other code paths run: 64-wide heads on the tensor-core kernel over twenty key tiles, windows that skip
+    tiles, a layer without a window whose decoding splits the keys, hundreds of pairs per expert through the grouped products."""
+    A = O.attn_layer
+    kw = dict(heads=8, kv_heads=2, dim=64, vdim=64, rot_dims=32, experts=8, identity=1, top=2, groups=(3, 2), ff=128, shared_ff=256)
+    cfg = O.make_config([A(window=200, keep_first=5, **kw), A(window=5000, keep_first=0, **kw), A(window=130, keep_first=70, kv_from=1, **kw)],
+                        width=256, vocab=300, buckets=211)
+    W = O.random_model(cfg, seed=21)
+    toks = tokens(1320, 300, 4)
+    rows = list(range(0, 1300, 97)) + [1297, 1298, 1299]
+    want = O.forward(cfg, W, toks)
+    for dtype in (F32, BF16):
+        m = load(tmp_path, cfg, W, dtype, str(dtype)[-4:])
+        seq = m.new_sequence()
+        got = [m.step([(seq, toks[:1300])], [rows])]
+        for p_ in range(1300, 1320):
+            got.append(m.step([(seq, [toks[p_]])]))
+        got = torch.cat(got)
+        ref = want[rows + list(range(1300, 1320))]
+        if dtype == F32:
+            close(got, ref, 1e-4, "medium model, float32")
+        else:
+            close_rows(got, ref, 5e-2, "medium model, bfloat16", share=0.7)
+        seq.free()
 
 
 def test_greedy_generation_through_the_engines(tmp_path):
