@@ -208,24 +208,24 @@ def kernel_block(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: flo
 # ---- Raritar ----------------------------------------------------------------------------------------------------------
 RARITAR_SIZES = {
     # width, heads / kv heads / dim / vdim, window, experts / pass-through / top / groups / expert ff / shared ff, layers, vocab
-    "w1024": dict(width=1024, H=8, G=2, D=128, V=128, window=512, keep=4, E=8, I=2, top=2, groups=(2, 1), ff=1024, sff=2048, layers=4, vocab=8192),
-    "w2048": dict(width=2048, H=16, G=4, D=128, V=128, window=1024, keep=4, E=16, I=0, top=4, groups=(4, 2), ff=1024, sff=4096, layers=8, vocab=8192),
+    "w1024": dict(width=1024, H=8, G=2, D=128, V=128, window=512, keep=8, E=8, I=2, top=2, groups=(2, 1), ff=1024, sff=2048, layers=4, vocab=8192),
+    "w2048": dict(width=2048, H=16, G=4, D=128, V=128, window=1024, keep=8, E=16, I=0, top=4, groups=(4, 2), ff=1024, sff=4096, layers=8, vocab=8192),
 }
 
 
 def raritar_config(s: dict) -> dict:
     def layer(kv_from=None):
-        mixer = {"heads": s["H"], "kv_heads": s["G"], "dim": s["D"], "vdim": s["V"], "scale": s["D"] ** -0.5, "softcap": 50.0,
+        mixer = {"heads": s["H"], "kv_heads": s["G"], "dim": s["D"], "vdim": s["V"], "scale": s["D"] ** -0.5, "softcap": 30.0,
                  "mask": {"size": s["window"], "keep_first": s["keep"]},
-                 "rot": {"base": 10000.0, "dims": s["D"] // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+                 "rot": {"base": 10000.0, "dims": s["D"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}}
         if kv_from is not None:
             mixer["kv_from"] = kv_from
         mlp = {"kind": "moe", "expert": {"ff": s["ff"]}, "shared": {"ff": s["sff"]},
                "router": {"experts": s["E"], "identity": s["I"], "top": s["top"], "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
         return {"type": "attention", "mixer": mixer, "mlp": mlp}
     own = s["layers"] - s["layers"] // 4       # the last quarter of the layers reads the rows of the last layer that has its own
-    return {"architecture": "Raritar", "vocab": s["vocab"], "width": s["width"], "residual_mult": 0.7, "norm": {"eps": 1e-5},
-            "canon": {"taps": 4}, "embedding": {"bigram": {"buckets": 4093, "mul_prev": 31, "mul_cur": 7}},
+    return {"architecture": "Raritar", "vocab": s["vocab"], "width": s["width"], "residual_mult": 0.8, "norm": {"eps": 1e-5},
+            "canon": {"taps": 3}, "embedding": {"bigram": {"buckets": 4093, "mul_prev": 29, "mul_cur": 5}},
             "layers": [layer() for _ in range(own)] + [layer(own - 1) for _ in range(s["layers"] - own)]}
 
 
@@ -314,9 +314,9 @@ def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: 
     q, o = torch.randn(prompt, H * D, device=dev).to(bf), torch.empty(prompt, H * V, device=dev, dtype=bf)
     # prompt attention: FLOPs = 2 (D + V) per (query, VISIBLE key) pair and head
     pairs = sum(min(i + 1, win) + max(0, min(keep, i + 1 - win)) for i in range(prompt))
-    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, softcap=50.0, window=win, keep_first=keep))
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, softcap=30.0, window=win, keep_first=keep))
     out["attn_prompt_window"] = tf(2.0 * (D + V) * H * pairs, ms)
-    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, softcap=50.0))
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, softcap=30.0))
     out["attn_prompt_capped_full"] = tf(2.0 * (D + V) * H * prompt * (prompt + 1) / 2, ms)
     ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b))
     out["like_attn_prompt_full"] = tf(2.0 * (D + V) * H * prompt * (prompt + 1) / 2, ms)
@@ -324,18 +324,18 @@ def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: 
     b1 = nsq.Batch([0], [ctx], [1], dev)
     q1, o1 = torch.randn(1, H * D, device=dev).to(bf), torch.empty(1, H * V, device=dev, dtype=bf)
     wsd = nsq.attn_workspace(1, H, V, dev)
-    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, None, None, False, b1, max_keys=win + keep, workspace=wsd, softcap=50.0, window=win,
+    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, None, None, False, b1, max_keys=win + keep, workspace=wsd, softcap=30.0, window=win,
                                      keep_first=keep), steps=15)
     out["attn_decode_window"] = gb(2.0 * G * (win + keep) * (D + V), ms)
     ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, None, None, False, b1, max_keys=cap, workspace=wsd), steps=15)
     out["like_attn_decode_full"] = gb(2.0 * G * (ctx + 1) * (D + V), ms)
     # norm + convolution: reads x (4 B, neighbours from L2) and writes h (2 B); like: gated norm + residual + next norm
     x, h = torch.randn(prompt, W, device=dev), torch.empty(prompt, W, device=dev, dtype=bf)
-    g1, cw, tail = torch.ones(1, device=dev, dtype=bf), (torch.randn(4, W, device=dev) * 0.3).to(bf), torch.zeros(1, 2, 3, W, device=dev)
+    g1, cw, tail = torch.ones(1, device=dev, dtype=bf), (torch.randn(3, W, device=dev) * 0.3).to(bf), torch.zeros(1, 2, 2, W, device=dev)
     ms = timer(lambda: nsq.norm_conv(x, g1, 1e-5, h, conv_w=cw, tail=tail, batch=b))
     out["norm_conv"] = gb(prompt * W * 6.0, ms)
     y = torch.randn(prompt, W, device=dev).to(bf)
-    ms = timer(lambda: nsq.norm_conv(x, g1, 1e-5, h, y=y, y_mult=0.7))
+    ms = timer(lambda: nsq.norm_conv(x, g1, 1e-5, h, y=y, y_mult=0.8))
     out["add_norm"] = gb(prompt * W * 12.0, ms)
     wn = torch.ones(W, device=dev, dtype=bf)
     ms = timer(lambda: nsq.gate_norm_add(x, y, None, wn, None, 1e-5, wn, h))
@@ -375,7 +375,7 @@ def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: 
     ms = timer(lambda: nsq.linear(hb[:1], wl, kernel=True), steps=15)
     out["like_linear_rows"] = gb(real1 * 3.0 * ff * W * 2, ms)
     ye, wg2, sg, ys = torch.randn(prompt * top, W, device=dev), torch.rand(prompt, top, device=dev), torch.rand(prompt, device=dev), torch.randn(prompt, W, device=dev).to(bf)
-    ms = timer(lambda: nsq.moe_combine(x, ye, idx, wg2, hb, E, 0.7, ys=ys, shared_gate=sg))
+    ms = timer(lambda: nsq.moe_combine(x, ye, idx, wg2, hb, E, 0.8, ys=ys, shared_gate=sg))
     out["moe_combine"] = gb(prompt * W * (4.0 * top + 2 + 8), ms)
     return out
 

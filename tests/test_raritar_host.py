@@ -69,7 +69,7 @@ def test_oracle_is_causal_and_windowed():
     assert torch.allclose(O.forward(cfg, W, toks[:7]), full[:7], atol=1e-12)
     assert O.visible(10, 6, 5, 1) and not O.visible(10, 5, 5, 1) and O.visible(10, 0, 5, 1) and not O.visible(10, 1, 5, 1)
     assert not O.visible(3, 4, 5, 1)
-    assert O.bigram_rows([4, 5, 6], 11, 31, 7) == [11, (4 * 31 + 5 * 7) % 11, (5 * 31 + 6 * 7) % 11]
+    assert O.bigram_rows([4, 5, 6], 11, 29, 5) == [11, (4 * 29 + 5 * 5) % 11, (5 * 29 + 6 * 5) % 11]
     z = torch.tensor([0.1, 2.0, 0.3, 1.9, -1.0, 0.0], dtype=O.F64)
     chosen, w = O.route(z, torch.zeros(6, dtype=O.F64), 2, 3, 1)
     assert chosen == [1, 0]                  # only the best group (outputs 0, 1) can be chosen, although output 3 scores higher than 0
